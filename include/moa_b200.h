@@ -1,0 +1,140 @@
+/*
+ * moa_b200 — C ABI of the B200 (sm_100a) kernels for MoA's attention hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the CUDA
+ * stream it is given, never synchronises the device and never allocates device memory.
+ * The return value is a moa_status (0 = MOA_OK); moa_strerror() names it and
+ * moa_last_error_detail() gives the CUDA error text of the calling thread's last failure.
+ *
+ * The comment on each function names the part of thu-nics/MoA it stands in for
+ * (paths relative to that repository).
+ */
+#ifndef MOA_B200_H_
+#define MOA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOA_ABI_VERSION 1
+
+typedef void* moa_stream_t; /* a cudaStream_t; NULL is the legacy default stream */
+
+enum moa_dtype { MOA_F16 = 0, MOA_BF16 = 1 };
+
+enum moa_status {
+  MOA_OK = 0,
+  MOA_ERR_INVALID_ARG = 1,  /* null pointer, bad shape or stride                         */
+  MOA_ERR_UNSUPPORTED = 2,  /* head_dim or dtype the kernels are not built for            */
+  MOA_ERR_CUDA = 3,         /* a CUDA runtime/driver call failed; see moa_last_error_detail */
+  MOA_ERR_WORKSPACE = 4,    /* workspace missing or too small                            */
+  MOA_ERR_DEVICE_WAIT = 5,  /* a bounded wait inside a kernel ran out (reported via status word) */
+  MOA_ERR_TOO_LARGE = 6     /* size beyond a fixed limit of the entry point              */
+};
+
+int moa_abi_version(void);
+const char* moa_strerror(int status);
+const char* moa_last_error_detail(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode: flash-decoding over the per-head ring caches of one layer.
+ *
+ * Replaces the external `flashinfer.moa_decode(q, k, v, head_start_index, head_valid_length,
+ * sm_scale)` call at MoA/kernels/mixture_of_attention.py:465-473 and, when k_new/v_new are
+ * given, also the decode branch of StaticCircularCache.update
+ * (MoA/attention/cache_utils.py:1020-1058) in the same launch.
+ *
+ *   q            (B, H, D)   contiguous; the reference's (B,H,1,D) and (B,1,H,D) are this memory
+ *   k_cache,
+ *   v_cache      (B, S, D)   contiguous, S = sum of per-head capacities; head h owns rows
+ *                            [head_start[b,h], head_start[b,h+1]) (last head: up to S)
+ *   k_new, v_new (B, H, D)   both NULL: attention only over the first valid_len[b,h] rows of
+ *                            each head.  Both non-NULL: fused append — the new row is written at
+ *                            update_index[b,h], attention runs over the rows that are valid
+ *                            after the append (the new token is attended), and afterwards
+ *                            valid_len, update_index and mask_cache are advanced exactly as
+ *                            cache_utils.py:1031-1054 does (kv_len is the layer's _kv_len
+ *                            before this step; static_size is static_cache_size[layer]).
+ *   out          element (b, h, d) is written at out[b*out_batch_stride + h*out_head_stride + d]
+ *                            so (B,1,H,D) and a slice of a wider gather buffer are both possible
+ *   head_start,
+ *   valid_len,
+ *   update_index (B, H) int64;  mask_cache (B, S) int64 or NULL;  static_size (H) int64
+ *   workspace    moa_decode_workspace_bytes() bytes, zeroed once by
+ *                moa_decode_workspace_init(); reusable by later calls on the same stream.
+ *                Two launches that overlap in time must not share a workspace.
+ *   chunk        rows of the flattened cache per thread block; 0 picks the default.
+ * ------------------------------------------------------------------------------------------ */
+int64_t moa_decode_workspace_bytes(int B, int H, int D, int64_t S, int chunk);
+int moa_decode_workspace_init(void* workspace, int64_t workspace_bytes, moa_stream_t stream);
+int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                   void* out, int64_t out_batch_stride, int64_t out_head_stride,
+                   const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                   int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                   int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                   void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Ring-cache bookkeeping (StaticCircularCache.update, MoA/attention/cache_utils.py:953-1164).
+ *
+ * moa_cache_append: decode branch (:1020-1058) without attention.  k_new/v_new (B,H,D) with
+ *   element strides nk_b, nk_h (row of D contiguous); NULL k_new/v_new = the reference's
+ *   update_cache_content=False (indices, lengths and mask advance, payload untouched).
+ *
+ * moa_cache_scan_mask: for the prefill branch with an attention mask (:1062-1086).
+ *   mask (B, N) int64 with row stride mask_stride; writes pos (B, N) int32 = position of the
+ *   j-th unmasked token of the row, and count (B) int32 = number of unmasked tokens.
+ *
+ * moa_cache_fill: prefill branch (:1060-1164).  k, v (B,H,N,D) with element strides
+ *   (sb, sh, sn; D contiguous).  pos/count from moa_cache_scan_mask, or both NULL for "no
+ *   mask".  Keeps a token iff it is among the last circ_h unmasked tokens or its slot lies
+ *   in the static part (:1122-1133); advances valid_len (+= kept), update_index (:1110) and
+ *   mask_cache (:1149).  max_cap = largest per-head capacity (sizes the grid).
+ * ------------------------------------------------------------------------------------------ */
+int moa_cache_append(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                     int64_t new_batch_stride, int64_t new_head_stride,
+                     const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                     int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                     int B, int H, int D, int64_t S, int dtype, moa_stream_t stream);
+int moa_cache_scan_mask(const int64_t* mask, int64_t mask_stride, int32_t* pos, int32_t* count,
+                        int B, int64_t N, moa_stream_t stream);
+int moa_cache_fill(const void* k, const void* v, int64_t sb, int64_t sh, int64_t sn,
+                   void* k_cache, void* v_cache, const int32_t* pos, const int32_t* count,
+                   const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                   int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                   int B, int H, int64_t N, int D, int64_t S, int64_t max_cap, int dtype,
+                   moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Prefill: causal sink + sliding-window block-sparse attention.
+ *
+ * Replaces `flashinfer.moa_prefill(q, k, v, causal=True, num_global_blocks, num_band_blocks,
+ * kv_layout="HND")` (MoA/kernels/mixture_of_attention.py:435-444) and the Triton kernel
+ * `_sparse_attention_prefill_moa_fwd_kernel` (MoA/kernels/block_sparse_attention_prefill.py:
+ * 473-696): q-block bi (64 rows) sees kv-block j iff j <= bi and (j < sink_blocks[h] or
+ * j >= bi + 1 - local_blocks[h]); inside a block the mask is causal.
+ *
+ *   q, k, v  (B, H, N, D) with byte-aligned element strides (sb, sh, sn), D contiguous,
+ *            every stride a multiple of 8 elements, base pointers 16-byte aligned
+ *   out      written as out[b*ob + n*on + h*oh + d]; (B,N,H,D) contiguous is ob=N*H*D, on=H*D, oh=D
+ *   sink_blocks, local_blocks (H) int32 device arrays, in 64-token blocks
+ *   status   device int32[4], zero on entry; a non-zero word after the kernel finished means a
+ *            bounded wait inside the kernel gave up (MOA_ERR_DEVICE_WAIT) and out is invalid
+ *   out_f32  non-zero: out is float32 (same math, fp32 store) — used to check the bf16 path
+ * ------------------------------------------------------------------------------------------ */
+int moa_prefill_fwd(const void* q, const void* k, const void* v, void* out,
+                    int64_t q_sb, int64_t q_sh, int64_t q_sn,
+                    int64_t k_sb, int64_t k_sh, int64_t k_sn,
+                    int64_t v_sb, int64_t v_sh, int64_t v_sn,
+                    int64_t o_sb, int64_t o_sn, int64_t o_sh,
+                    const int32_t* sink_blocks, const int32_t* local_blocks,
+                    int B, int H, int64_t N, int D, float sm_scale, int dtype, int out_f32,
+                    int32_t* status, moa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOA_B200_H_ */

@@ -1,0 +1,333 @@
+// Split-K flash-decoding over per-head ring caches, with the ring append fused in.
+//
+// Work decomposition: the flattened cache axis (B, S = sum of head capacities) is cut into
+// fixed-size chunks of `chunk` rows; thread block (c, b) streams the rows of chunk c of batch
+// row b.  Every block therefore moves the same number of bytes when the rings are full, however
+// different the heads' capacities are, and no work table is needed: the block finds the head(s)
+// its chunk overlaps from head_start[b, :].  For each overlapped head it produces a partial
+// (max, sum, o[D]) in fp32; the last block to finish a head (atomic ticket) merges that head's
+// partials, writes the output row and — in fused-append mode — advances the ring metadata.  No
+// block ever waits for another one.
+//
+// Memory traffic per step is the algorithmic minimum (every valid K and V row once) plus
+// (D+4)*4 bytes of partials per (head, chunk).
+#include "common.cuh"
+
+namespace moa {
+namespace {
+
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kTileIters = 8;  // 16-byte loads of K (and of V) in flight per thread
+constexpr int kDefaultChunk = 128;
+
+struct DecodeParams {
+  const void* q;
+  void* k_cache;
+  void* v_cache;
+  const void* k_new;
+  const void* v_new;
+  void* out;
+  int64_t out_bs, out_hs;
+  const int64_t* head_start;
+  int64_t* valid_len;
+  int64_t* update_index;
+  int64_t* mask_cache;
+  const int64_t* static_size;
+  int64_t kv_len;
+  int B, H;
+  int64_t S;
+  float scale_log2;  // sm_scale * log2(e)
+  int* tickets;      // (B, H), zero between launches
+  float* partials;   // (B, nchunks + H, D + 4)
+  int64_t slots_per_batch;
+  int chunk;
+};
+
+__host__ __device__ inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// Largest h with head_start[h] <= row (head_start ascending); every lane returns the result.
+__device__ __forceinline__ int find_head(const int64_t* hs, int H, int64_t row, int lane) {
+  int count = 0;
+  for (int base = 0; base < H; base += 32) {
+    const int h = base + lane;
+    const bool le = (h < H) && (hs[h] <= row);
+    count += __popc(__ballot_sync(0xffffffffu, le));
+  }
+  return count > 0 ? count - 1 : 0;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const DecodeParams p) {
+  constexpr int LPR = D / 8;    // lanes that share one cache row (16 bytes each)
+  constexpr int RPI = 32 / LPR; // rows a warp covers with one load instruction
+  constexpr int TILE = RPI * kTileIters;
+  constexpr int GROUPS = kDecodeWarps * RPI;
+  constexpr int REC = D + 4;
+  static_assert(D == 64 || D == 128, "head_dim");
+
+  __shared__ float sm_m[GROUPS];
+  __shared__ float sm_l[GROUPS];
+  __shared__ __align__(16) float sm_acc[GROUPS][D];
+  __shared__ int sm_last;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub = lane / LPR, li = lane % LPR;
+  const int b = blockIdx.y;
+  const int64_t c = blockIdx.x;
+  const int64_t lo = c * p.chunk;
+  const int64_t hi = min(lo + (int64_t)p.chunk, p.S);
+  const int64_t* hs_row = p.head_start + (int64_t)b * p.H;
+  const bool fused = p.k_new != nullptr;
+
+  const T* kc = reinterpret_cast<const T*>(p.k_cache) + (int64_t)b * p.S * D;
+  const T* vc = reinterpret_cast<const T*>(p.v_cache) + (int64_t)b * p.S * D;
+
+  for (int h = find_head(hs_row, p.H, lo, lane); h < p.H; ++h) {
+    const int64_t hs = hs_row[h];
+    if (hs >= hi) break;
+    const int64_t he = (h + 1 < p.H) ? hs_row[h + 1] : p.S;
+    if (he <= lo || he <= hs) continue;
+    const int64_t cap = he - hs;
+    const int64_t bh = (int64_t)b * p.H + h;
+    const int64_t valid_pre = p.valid_len[bh];
+    const int64_t upd = fused ? p.update_index[bh] : -1;
+    const int64_t valid_post = fused ? valid_pre + (valid_pre < cap ? 1 : 0) : valid_pre;
+    const int64_t seg_lo = max(lo, hs);
+    const int64_t seg_hi = min(hi, hs + valid_post);
+    const T* knew = fused ? reinterpret_cast<const T*>(p.k_new) + bh * D : nullptr;
+    const T* vnew = fused ? reinterpret_cast<const T*>(p.v_new) + bh * D : nullptr;
+
+    // Fused append: the block whose chunk holds the write slot stores the new K and V rows.
+    // No other block reads that row (it lies in this chunk only), and this block takes the row's
+    // values from k_new/v_new below, so the store does not race with any load.
+    if (fused && upd >= lo && upd < hi && upd >= hs && upd < he && warp == 0 && lane < 2 * LPR) {
+      const bool is_v = lane >= LPR;
+      const int l16 = lane % LPR;
+      const T* src = (is_v ? vnew : knew) + l16 * 8;
+      T* dst = const_cast<T*>(is_v ? vc : kc) + upd * D + l16 * 8;
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    }
+
+    // q slice of this lane, pre-scaled so that softmax runs in base 2
+    float qf[8];
+    {
+      const uint4 qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + bh * D + li * 8);
+      unpack8<T>(qu, qf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qf[j] *= p.scale_log2;
+    }
+
+    float m = -INFINITY, l = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+
+    for (int64_t row0 = seg_lo + (int64_t)warp * TILE; row0 < seg_hi; row0 += (int64_t)kDecodeWarps * TILE) {
+      uint4 kr[kTileIters], vr[kTileIters];
+#pragma unroll
+      for (int i = 0; i < kTileIters; ++i) {
+        // rows past the segment re-read its last row (a valid address); their score is masked
+        const int64_t r = min(row0 + i * RPI + sub, seg_hi - 1);
+        kr[i] = ld_stream16((r == upd) ? knew + li * 8 : kc + r * D + li * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < kTileIters; ++i) {
+        const int64_t r = min(row0 + i * RPI + sub, seg_hi - 1);
+        vr[i] = ld_stream16((r == upd) ? vnew + li * 8 : vc + r * D + li * 8);
+      }
+      float s[kTileIters];
+      float mt = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kTileIters; ++i) {
+        float kf[8];
+        unpack8<T>(kr[i], kf);
+        float d = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d = fmaf(qf[j], kf[j], d);
+#pragma unroll
+        for (int off = LPR / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        const int64_t r = row0 + i * RPI + sub;
+        s[i] = (r < seg_hi) ? d : -INFINITY;
+        mt = fmaxf(mt, s[i]);
+      }
+      const float m_new = fmaxf(m, mt);
+      if (m_new != -INFINITY) {
+        const float corr = exp2f(m - m_new);  // m == -inf gives 0
+        l *= corr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= corr;
+#pragma unroll
+        for (int i = 0; i < kTileIters; ++i) {
+          const float pr = exp2f(s[i] - m_new);  // masked rows give 0
+          l += pr;
+          float vf[8];
+          unpack8<T>(vr[i], vf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = fmaf(pr, vf[j], acc[j]);
+        }
+        m = m_new;
+      }
+    }
+
+    // combine the GROUPS running states of this block
+    const int g = warp * RPI + sub;
+    if (li == 0) {
+      sm_m[g] = m;
+      sm_l[g] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm_acc[g][li * 8 + j] = acc[j];
+    __syncthreads();
+
+    float M = -INFINITY;
+#pragma unroll
+    for (int gg = 0; gg < GROUPS; ++gg) M = fmaxf(M, sm_m[gg]);
+    float L = 0.f, O = 0.f;
+    if (M != -INFINITY) {
+      for (int gg = 0; gg < GROUPS; ++gg) {
+        const float w = exp2f(sm_m[gg] - M);
+        L += sm_l[gg] * w;
+        if (tid < D) O += sm_acc[gg][tid] * w;
+      }
+    }
+
+    const int64_t first_chunk = hs / p.chunk;
+    const int64_t nslots = (he - 1) / p.chunk - first_chunk + 1;
+    bool last = true;
+    if (nslots > 1) {
+      float* rec = p.partials + ((int64_t)b * p.slots_per_batch + c + h) * REC;
+      if (tid < D) rec[4 + tid] = O;
+      if (tid == 0) {
+        rec[0] = M;
+        rec[1] = L;
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) sm_last = (atomicAdd(&p.tickets[bh], 1) == (int)nslots - 1);
+      __syncthreads();
+      last = sm_last != 0;
+      if (last) {
+        __threadfence();
+        float Mg = -INFINITY;
+        for (int64_t sidx = 0; sidx < nslots; ++sidx) {
+          const float* r2 = p.partials + ((int64_t)b * p.slots_per_batch + first_chunk + sidx + h) * REC;
+          Mg = fmaxf(Mg, __ldcg(r2));
+        }
+        float Lg = 0.f, Og = 0.f;
+        if (Mg != -INFINITY) {
+          for (int64_t sidx = 0; sidx < nslots; ++sidx) {
+            const float* r2 = p.partials + ((int64_t)b * p.slots_per_batch + first_chunk + sidx + h) * REC;
+            const float w = exp2f(__ldcg(r2) - Mg);
+            Lg += __ldcg(r2 + 1) * w;
+            if (tid < D) Og += __ldcg(r2 + 4 + tid) * w;
+          }
+        }
+        L = Lg;
+        O = Og;
+        if (tid == 0) p.tickets[bh] = 0;  // ready for the next launch
+      }
+    }
+    if (last) {
+      if (tid < D) {
+        const float o = (L > 0.f) ? O / L : 0.f;
+        reinterpret_cast<T*>(p.out)[(int64_t)b * p.out_bs + (int64_t)h * p.out_hs + tid] = static_cast<T>(o);
+      }
+      if (fused && tid == 0) {
+        // every other block of this head has already read the old values (it took its ticket
+        // after reading them), so the metadata can advance now
+        p.valid_len[bh] = valid_post;
+        if (p.mask_cache) p.mask_cache[(int64_t)b * p.S + upd] = 1;
+        p.update_index[bh] = ring_next_index(upd, hs, cap, p.static_size[h], p.kv_len);
+      }
+    }
+    __syncthreads();  // shared buffers are reused by the next head of this chunk
+  }
+}
+
+template <typename T>
+int launch_decode(const DecodeParams& p, int D, dim3 grid, cudaStream_t stream) {
+  switch (D) {
+    case 64: moa_decode_kernel<T, 64><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+    case 128: moa_decode_kernel<T, 128><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+    default: set_error_text("decode: head_dim must be 64 or 128"); return MOA_ERR_UNSUPPORTED;
+  }
+  MOA_CUDA_CHECK(cudaGetLastError());
+  return MOA_OK;
+}
+
+struct WsLayout {
+  int64_t ticket_bytes, nchunks, slots_per_batch, total;
+};
+inline WsLayout ws_layout(int B, int H, int D, int64_t S, int chunk) {
+  WsLayout w;
+  w.ticket_bytes = round_up((int64_t)B * H * 4, 256);
+  w.nchunks = (S + chunk - 1) / chunk;
+  w.slots_per_batch = w.nchunks + H;
+  w.total = w.ticket_bytes + (int64_t)B * w.slots_per_batch * (D + 4) * 4;
+  return w;
+}
+
+}  // namespace
+
+// Validates the arguments, lays out the workspace and launches the kernel.
+int decode_launch_with_scratch(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                               void* out, int64_t out_bs, int64_t out_hs, const int64_t* head_start,
+                               int64_t* valid_len, int64_t* update_index, int64_t* mask_cache,
+                               const int64_t* static_size, int64_t kv_len, int B, int H, int D, int64_t S,
+                               float sm_scale, int dtype, void* workspace, int64_t workspace_bytes, int chunk,
+                               cudaStream_t stream) {
+  MOA_REQUIRE(q && k_cache && v_cache && out && head_start && valid_len, "decode: null pointer");
+  MOA_REQUIRE((k_new == nullptr) == (v_new == nullptr), "decode: k_new and v_new must both be given or both be NULL");
+  MOA_REQUIRE(B > 0 && H > 0 && S > 0 && B <= 65535, "decode: bad shape");
+  if (k_new) MOA_REQUIRE(update_index && static_size, "decode: fused append needs update_index and static_size");
+  if (chunk <= 0) chunk = kDefaultChunk;
+  const WsLayout w = ws_layout(B, H, D, S, chunk);
+  if (!workspace || workspace_bytes < w.total) {
+    set_error_text("decode: workspace missing or smaller than moa_decode_workspace_bytes()");
+    return MOA_ERR_WORKSPACE;
+  }
+  MOA_REQUIRE(w.nchunks <= 2147483647LL, "decode: too many chunks");
+  DecodeParams p;
+  p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_new = k_new; p.v_new = v_new; p.out = out;
+  p.out_bs = out_bs; p.out_hs = out_hs; p.head_start = head_start; p.valid_len = valid_len;
+  p.update_index = update_index; p.mask_cache = mask_cache; p.static_size = static_size; p.kv_len = kv_len;
+  p.B = B; p.H = H; p.S = S; p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.tickets = reinterpret_cast<int*>(workspace);
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.ticket_bytes);
+  p.slots_per_batch = w.slots_per_batch; p.chunk = chunk;
+  dim3 grid((unsigned)w.nchunks, (unsigned)B);
+  if (dtype == MOA_F16) return launch_decode<__half>(p, D, grid, stream);
+  if (dtype == MOA_BF16) return launch_decode<__nv_bfloat16>(p, D, grid, stream);
+  set_error_text("decode: dtype must be MOA_F16 or MOA_BF16");
+  return MOA_ERR_UNSUPPORTED;
+}
+
+}  // namespace moa
+
+extern "C" {
+
+int64_t moa_decode_workspace_bytes(int B, int H, int D, int64_t S, int chunk) {
+  if (B <= 0 || H <= 0 || D <= 0 || S <= 0) return 0;
+  if (chunk <= 0) chunk = moa::kDefaultChunk;
+  return moa::ws_layout(B, H, D, S, chunk).total;
+}
+
+int moa_decode_workspace_init(void* workspace, int64_t workspace_bytes, moa_stream_t stream) {
+  MOA_REQUIRE(workspace && workspace_bytes > 0, "workspace_init: null workspace");
+  MOA_CUDA_CHECK(cudaMemsetAsync(workspace, 0, (size_t)workspace_bytes, (cudaStream_t)stream));
+  return MOA_OK;
+}
+
+int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new, void* out,
+                   int64_t out_batch_stride, int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
+                   int64_t* update_index, int64_t* mask_cache, const int64_t* static_size, int64_t kv_len, int B,
+                   int H, int D, int64_t S, float sm_scale, int dtype, void* workspace, int64_t workspace_bytes,
+                   int chunk, moa_stream_t stream) {
+  return moa::decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
+                                         head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H,
+                                         D, S, sm_scale, dtype, workspace, workspace_bytes, chunk,
+                                         (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -112,29 +112,35 @@ def prefill_attention_fp32(
     sink_blocks: Sequence[int],
     local_blocks: Sequence[int],
     row_chunk: int = 2048,
+    row_range: Optional[Tuple[int, int]] = None,
 ) -> torch.Tensor:
     """fp32 softmax(mask(q k^T * sm_scale)) v with the MoA mask.
 
     q, k, v: (B, H, N, D) any float dtype.  Returns (B, N, H, D) fp32, the layout
     ``mixture_of_sparse_attention`` returns (mixture_of_attention.py:399, 459).
-    Rows are processed in chunks so N = 64k stays within host memory.
+    Rows are processed in chunks so N = 64k stays within host memory.  ``row_range=(a, b)``
+    evaluates only query rows [a, b) and returns (B, b-a, H, D): long sequences are spot-checked
+    this way.
     """
     B, H, N, D = q.shape
-    out = torch.empty(B, N, H, D, dtype=torch.float32)
+    ra, rb = row_range if row_range is not None else (0, N)
+    out = torch.empty(B, rb - ra, H, D, dtype=torch.float32)
     for h in range(H):
         s_b, l_b = int(sink_blocks[h]), int(local_blocks[h])
-        kf = k[:, h].float()
-        vf = v[:, h].float()
-        for r0 in range(0, N, row_chunk):
-            r1 = min(N, r0 + row_chunk)
+        for r0 in range(ra, rb, row_chunk):
+            r1 = min(rb, r0 + row_chunk)
+            kf = k[:, h, :r1].float()
+            vf = v[:, h, :r1].float()
             # columns that can be visible to rows [r0, r1): sink blocks + band
             i = torch.arange(r0, r1)[:, None]
             j = torch.arange(0, r1)[None, :]
             vis = (j <= i) & (((j // BLOCK) <= s_b - 1) | ((j // BLOCK) >= (i // BLOCK) + 1 - l_b))
-            s = torch.matmul(q[:, h, r0:r1].float(), kf[:, :r1].transpose(-1, -2)) * sm_scale
-            s = s.masked_fill(~vis[None], float("-inf"))
+            keep = vis.any(dim=0)                      # drop columns no row of the chunk sees
+            cols = torch.nonzero(keep).flatten()
+            s = torch.matmul(q[:, h, r0:r1].float(), kf[:, cols].transpose(-1, -2)) * sm_scale
+            s = s.masked_fill(~vis[None][:, :, cols], float("-inf"))
             p = torch.softmax(s, dim=-1)
-            out[:, r0:r1, h] = torch.matmul(p, vf[:, :r1])
+            out[:, r0 - ra:r1 - ra, h] = torch.matmul(p, vf[:, cols])
     return out
 
 

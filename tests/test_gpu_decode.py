@@ -1,0 +1,191 @@
+"""Flash-decoding kernel vs the fp32 oracle, through the public API and the raw C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import moa_b200
+from moa_b200 import _lib
+from oracle import moa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+# fp16: the tolerance the project states (max-abs 2e-3, mean-rel 1e-3 against fp32).
+# bf16: the store alone costs about one bf16 ulp (7.8e-3 at |x|~1, ~1.4e-3 mean-rel), so the bound is wider.
+TOL = {torch.float16: (2e-3, 1e-3), torch.bfloat16: (1.6e-2, 4e-3)}
+
+
+def _close(out, ref, dtype, what=""):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    max_abs = (out - ref).abs().max().item()
+    mean_rel = ((out - ref).abs().mean() / ref.abs().mean().clamp_min(1e-12)).item()
+    a, r = TOL[dtype]
+    assert max_abs <= a and mean_rel <= r, f"{what}: max-abs {max_abs:.3e} mean-rel {mean_rel:.3e}"
+
+
+def _random_cache(B, caps, Dh, dtype, gen, full=False):
+    S = sum(caps)
+    k = torch.randn(B, S, Dh, generator=gen).to(dtype)
+    v = torch.randn(B, S, Dh, generator=gen).to(dtype)
+    starts = np.concatenate([[0], np.cumsum(caps)[:-1]])
+    hs = torch.tensor(np.tile(starts, (B, 1)), dtype=torch.int64)
+    if full:
+        valid = torch.tensor(np.tile(caps, (B, 1)), dtype=torch.int64)
+    else:
+        valid = torch.stack([torch.tensor([int(torch.randint(0, c + 1, (1,), generator=gen)) for c in caps])
+                             for _ in range(B)]).to(torch.int64)
+        valid[0, 0] = caps[0]
+        if B > 1:
+            valid[1, -1] = 0
+    return k, v, hs, valid
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Dh", [128, 64])
+@pytest.mark.parametrize("caps", [[128, 128, 256, 320], [5, 10, 333, 100, 7], [4160, 320, 2112], [64] * 9])
+def test_sparse_decode_matches_oracle(dtype, Dh, caps):
+    gen = torch.Generator().manual_seed(hash((Dh, len(caps))) % 1000)
+    B = 3
+    k, v, hs, valid = _random_cache(B, caps, Dh, dtype, gen)
+    q = torch.randn(B, len(caps), 1, Dh, generator=gen).to(dtype)
+    sm = Dh ** -0.5
+    ref = orc.decode_attention_fp32(q, k, v, hs, valid, sm)
+    out = moa_b200.mixture_of_sparse_attention(q.cuda(), k.cuda(), v.cuda(), sm, head_start_index=hs.cuda(),
+                                               head_valid_length=valid.cuda())
+    assert out.shape == (B, 1, len(caps), Dh) and out.dtype == dtype
+    _close(out, ref, dtype, f"caps={caps}")
+    # heads with nothing valid give zeros, not NaN
+    assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("chunk", [64, 96, 128, 256, 1000, 100000])
+def test_every_chunk_size_gives_the_same_answer(chunk):
+    """The split size only changes how partial sums are grouped; results agree to fp32 rounding."""
+    gen = torch.Generator().manual_seed(9)
+    caps, B, Dh, dtype = [320, 576, 1088, 128, 2112], 2, 128, torch.float16
+    k, v, hs, valid = _random_cache(B, caps, Dh, dtype, gen)
+    q = torch.randn(B, len(caps), 1, Dh, generator=gen).to(dtype)
+    ref = orc.decode_attention_fp32(q, k, v, hs, valid, 0.09)
+    qd, kd, vd, hsd, vald = q.cuda(), k.cuda(), v.cuda(), hs.cuda(), valid.cuda()
+    H, S = len(caps), sum(caps)
+    need = _lib.lib.moa_decode_workspace_bytes(B, H, Dh, S, chunk)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    out = torch.empty(B, 1, H, Dh, dtype=dtype, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):  # second call reuses the workspace (tickets reset themselves)
+        rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), out.stride(0),
+                                     out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0, B, H, Dh, S, 0.09, 0,
+                                     ws.data_ptr(), need, chunk, stream)
+        assert rc == 0, _lib.lib.moa_last_error_detail()
+        _close(out, ref, dtype, f"chunk={chunk}")
+    # too small a workspace is refused, not overrun
+    rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), out.stride(0),
+                                 out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0, B, H, Dh, S, 0.09, 0,
+                                 ws.data_ptr(), need - 1, chunk, stream)
+    assert rc == 4
+
+
+def test_reference_sdpa_decode_fixture():
+    """Prefill 400 tokens, three decode steps; outputs recorded from the reference's "sdpa" path."""
+    g = np.load(os.path.join(GOLDEN, "decode_sdpa.npz"))
+    caps = g["caps"].tolist()
+    B, H, Dh = 2, len(caps), 128
+    cache = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", torch.float16)
+    cache.update(torch.from_numpy(g["k_prefill"]).cuda(), torch.from_numpy(g["v_prefill"]).cuda(), 0)
+    sm = float(g["sm_scale"])
+    for s in range(g["q"].shape[0]):
+        q = torch.from_numpy(g["q"][s]).cuda()
+        kc, vc = cache.update(torch.from_numpy(g["k_new"][s]).cuda(), torch.from_numpy(g["v_new"][s]).cuda(), 0)
+        out = moa_b200.mixture_of_sparse_attention(q, kc, vc, sm, head_start_index=cache.cache_head_start_index[0],
+                                                   head_valid_length=cache.cache_valid_length[0])
+        _close(out, torch.from_numpy(g["out"][s]), torch.float16, f"step {s}")
+    assert np.array_equal(cache.key_cache[0].cpu().numpy(), g["key_cache_final"])
+    assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), g["update_index_final"])
+
+
+def test_out_may_be_a_slice_of_a_gather_buffer():
+    gen = torch.Generator().manual_seed(2)
+    caps, B, Dh = [128, 256], 2, 128
+    cache = moa_b200.StaticCircularCache([caps], B, Dh, [[64, 64]], "cuda", torch.float16)
+    kp = torch.randn(B, 2, 300, Dh, generator=gen).half().cuda()
+    cache.update(kp, kp, 0)
+    q, k1, v1 = (torch.randn(B, 2, 1, Dh, generator=gen).half().cuda() for _ in range(3))
+    gather = torch.zeros(B, 1, 6, Dh, dtype=torch.float16, device="cuda")
+    state = (cache.cache_update_index[0].clone(), cache.cache_valid_length[0].clone(), cache.key_cache[0].clone(),
+             cache.value_cache[0].clone(), cache.mask_cache[0].clone(), cache._kv_len[0])
+    ref = cache.decode_attention(q, k1, v1, 0, 0.1)
+    cache.cache_update_index[0].copy_(state[0]); cache.cache_valid_length[0].copy_(state[1])
+    cache.key_cache[0].copy_(state[2]); cache.value_cache[0].copy_(state[3]); cache.mask_cache[0].copy_(state[4])
+    cache._kv_len[0] = state[5]
+    cache.decode_attention(q, k1, v1, 0, 0.1, out=gather[:, :, 2:4])
+    assert torch.equal(gather[:, :, 2:4], ref)
+    assert gather[:, :, :2].abs().sum() == 0 and gather[:, :, 4:].abs().sum() == 0
+
+
+def test_config1_rings_wrap_and_match_oracle():
+    """BASELINE config 1 at reduced batch: 32 heads, windows from {256..4096} + 64 sinks, caches
+    filled from a 16k-token stream, 256 fused decode steps; every ring crosses its end at step 64."""
+    gen = torch.Generator().manual_seed(1001)
+    B, H, Dh, N, steps = 2, 32, 128, 16384, 256
+    W = sorted(int(w) for w in np.random.RandomState(1).choice([256, 512, 1024, 2048, 4096], H))
+    caps = [64 + w for w in W]
+    o = orc.RingCacheOracle([caps], [[64] * H], B, Dh, dtype=np.float16)
+    c = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", torch.float16)
+    k = torch.randn(B, H, N, Dh, generator=gen).half()
+    v = torch.randn(B, H, N, Dh, generator=gen).half()
+    o.update(k.numpy(), v.numpy(), 0)
+    c.update(k.cuda(), v.cuda(), 0)
+    assert np.array_equal(c.key_cache[0].cpu().numpy(), o.key_cache[0])
+    starts = o.head_index[0][:-1]
+    assert np.array_equal(o.cache_update_index[0][0] - starts - 64, np.asarray(W) - 64)
+    sm = Dh ** -0.5
+    crossings = np.zeros(H, dtype=np.int64)
+    check_at = {0, 1, 63, 64, 65, 128, 255}
+    for step in range(steps):
+        q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen).half() for _ in range(3))
+        before = o.cache_update_index[0][0].copy()
+        kc, vc = o.update(k1.numpy(), v1.numpy(), 0)
+        crossings += (o.cache_update_index[0][0] < before)
+        out = c.decode_attention(q.cuda(), k1.cuda(), v1.cuda(), 0, sm)
+        if step in check_at:
+            ref = orc.decode_attention_fp32(q, torch.from_numpy(kc), torch.from_numpy(vc),
+                                            torch.from_numpy(o.cache_head_start_index[0]),
+                                            torch.from_numpy(o.cache_valid_length[0]), sm)
+            _close(out, ref, torch.float16, f"step {step}")
+            assert np.array_equal(c.cache_update_index[0].cpu().numpy(), o.cache_update_index[0])
+    assert (crossings == 1).all()
+    assert np.array_equal(c.key_cache[0].cpu().numpy(), o.key_cache[0])
+    assert np.array_equal(c.value_cache[0].cpu().numpy(), o.value_cache[0])
+    assert np.array_equal(c.cache_valid_length[0].cpu().numpy(), o.cache_valid_length[0])
+
+
+def test_full_size_config1_properties():
+    """Batch 16 x 32 heads at full capacities (445 MB of K/V): size-independent checks.
+    (1) V == per-dim constant  =>  output == that constant (weights sum to one);
+    (2) every head with a one-hot q.k winner returns that slot's V row."""
+    B, H, Dh = 16, 32, 128
+    W = sorted(int(w) for w in np.random.RandomState(1).choice([256, 512, 1024, 2048, 4096], H))
+    caps = [64 + w for w in W]
+    S = sum(caps)
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    k = torch.randn(B, S, Dh, generator=gen, device="cuda").half()
+    const = torch.linspace(-2, 2, Dh, device="cuda").half()
+    v = const[None, None, :].expand(B, S, Dh).contiguous()
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(caps)[:-1]]), device="cuda")
+    hs = starts[None].expand(B, H).contiguous()
+    valid = torch.tensor(caps, device="cuda")[None].expand(B, H).contiguous()
+    q = torch.randn(B, H, 1, Dh, generator=gen, device="cuda").half()
+    out = moa_b200.mixture_of_sparse_attention(q, k, v, Dh ** -0.5, head_start_index=hs, head_valid_length=valid)
+    assert (out.float() - const.float()[None, None, None]).abs().max() < 2e-3
+    # one-hot winner: slot w of each head has key == 30*q/|q|^2-ish, the others ~0
+    k2 = torch.zeros(B, S, Dh, device="cuda", dtype=torch.float16)
+    v2 = torch.randn(B, S, Dh, generator=gen, device="cuda").half()
+    win = (starts + torch.tensor([c // 3 for c in caps], device="cuda"))
+    qn = q[:, :, 0] / (q[:, :, 0].float().pow(2).sum(-1, keepdim=True)).half()
+    bidx = torch.arange(B, device="cuda")[:, None].expand(B, H)
+    k2[bidx, win[None].expand(B, H)] = (qn.float() * 400).half()
+    out2 = moa_b200.mixture_of_sparse_attention(q, k2, v2, 1.0, head_start_index=hs, head_valid_length=valid)
+    want = v2[bidx, win[None].expand(B, H)]
+    assert (out2[:, 0].float() - want.float()).abs().max() < 2e-3

@@ -1,0 +1,187 @@
+"""Block-sparse prefill kernel (tcgen05/TMEM/TMA) vs the fp32 oracle and the reference fixtures."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import moa_b200
+from oracle import moa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _err(out, ref):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    return (out - ref).abs().max().item(), ((out - ref).abs().mean() / ref.abs().mean().clamp_min(1e-12)).item()
+
+
+def _close(out, ref, what="", max_abs=2e-3, mean_rel=1e-3):
+    a, r = _err(out, ref)
+    assert a <= max_abs and r <= mean_rel, f"{what}: max-abs {a:.3e} mean-rel {r:.3e}"
+
+
+def _run(q, k, v, sm, sink_b, local_b, **kw):
+    out = moa_b200.sparse_prefill(q.cuda(), k.cuda(), v.cuda(), sm,
+                                  torch.as_tensor(sink_b, dtype=torch.int32).cuda(),
+                                  torch.as_tensor(local_b, dtype=torch.int32).cuda(), **kw)
+    moa_b200.check_device_status()
+    return out
+
+
+def test_reference_triton_fixture_sparse():
+    g = np.load(os.path.join(GOLDEN, "prefill_sparse.npz"))
+    q, k, v = (torch.from_numpy(g[x]) for x in "qkv")
+    out = _run(q, k, v, float(g["sm_scale"]), g["sink_blocks"], g["local_blocks"])
+    assert out.shape == (1, 320, 3, 128) and out.is_contiguous()
+    _close(out, torch.from_numpy(g["masked_fp32"]), "vs fp32 under the reference-built mask")
+    _close(out, torch.from_numpy(g["triton_fp16"]), "vs the reference Triton kernel", 3e-3, 1.5e-3)
+
+
+def test_reference_triton_fixture_ragged():
+    g = np.load(os.path.join(GOLDEN, "prefill_ragged.npz"))
+    q, k, v = (torch.from_numpy(g[x]) for x in "qkv")
+    out = _run(q, k, v, float(g["sm_scale"]), g["sink_blocks"], g["local_blocks"])
+    ref = orc.prefill_attention_fp32(q, k, v, float(g["sm_scale"]), g["sink_blocks"], g["local_blocks"])
+    _close(out, ref, "ragged N=200 vs fp32")
+    _close(out, torch.from_numpy(g["triton_fp16"]), "ragged vs Triton", 3e-3, 1.5e-3)
+
+
+def test_reference_own_prefill_test_through_public_entry():
+    """tests/attention_kernel_test.py:35-76 of the reference: B2 H4 N128 D128, torch.rand data,
+    sm_scale 0.1, sink = local = 64 tokens, compared at rtol = atol = 1e-3."""
+    g = np.load(os.path.join(GOLDEN, "prefill_reftest.npz"))
+    q, k, v = (torch.from_numpy(g[x]).cuda() for x in "qkv")
+    out = moa_b200.mixture_of_sparse_attention(q, k, v, 0.1, attention_dropout=0.0, implementation="moa",
+                                               local_size=torch.from_numpy(g["local_size"]).cuda(),
+                                               sink_size=torch.from_numpy(g["sink_size"]).cuda())
+    moa_b200.check_device_status()
+    assert out.shape == (2, 128, 4, 128)
+    torch.testing.assert_close(out.cpu(), torch.from_numpy(g["sdpa"]), rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(out.cpu(), torch.from_numpy(g["moa"]), rtol=1e-3, atol=1e-3)
+
+
+CASES = [
+    # B, H, N, sink_blocks, local_blocks
+    (1, 1, 64, [1], [1]),
+    (1, 2, 65, [1, 0], [1, 2]),
+    (2, 2, 128, [1, 1], [1, 2]),
+    (1, 3, 129, [1, 2, 0], [1, 1, 3]),
+    (1, 4, 256, [1, 1, 0, 3], [1, 2, 1, 4]),
+    (2, 3, 1000, [1, 1, 2], [2, 5, 40]),
+    (1, 4, 2048, [1, 1, 1, 0], [1, 3, 8, 31]),
+    (1, 2, 1, [1, 1], [1, 1]),
+    (1, 2, 37, [1, 1], [1, 1]),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"B{c[0]}H{c[1]}N{c[2]}" for c in CASES])
+def test_fp16_random_against_oracle(case):
+    B, H, N, sink_b, local_b = case
+    gen = torch.Generator().manual_seed(N * 7 + H)
+    q, k, v = (torch.randn(B, H, N, 128, generator=gen).half() for _ in range(3))
+    sm = 128 ** -0.5
+    out = _run(q, k, v, sm, sink_b, local_b)
+    ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b)
+    assert out.shape == (B, N, H, 128)
+    _close(out, ref, str(case))
+
+
+def test_large_scores_force_rescaling():
+    """Keys whose scores grow along the sequence make the running max move in every tile."""
+    gen = torch.Generator().manual_seed(3)
+    B, H, N = 1, 2, 512
+    q = torch.randn(B, H, N, 128, generator=gen).half()
+    k = (torch.randn(B, H, N, 128, generator=gen) * torch.linspace(0.2, 6.0, N)[None, None, :, None]).half()
+    v = torch.randn(B, H, N, 128, generator=gen).half()
+    sm = 128 ** -0.5
+    out = _run(q, k, v, sm, [1, 1], [8, 2])
+    ref = orc.prefill_attention_fp32(q, k, v, sm, [1, 1], [8, 2])
+    _close(out, ref, "rescale", 3e-3, 1.5e-3)
+
+
+def test_strided_inputs_as_the_projection_produces_them():
+    gen = torch.Generator().manual_seed(8)
+    B, H, N = 2, 3, 300
+    # (B, N, H, D) storage viewed as (B, H, N, D): modeling_llama.py:238-240 of the reference
+    q, k, v = (torch.randn(B, N, H, 128, generator=gen).half().cuda().transpose(1, 2) for _ in range(3))
+    assert not q.is_contiguous()
+    sm = 128 ** -0.5
+    out = moa_b200.sparse_prefill(q, k, v, sm, torch.tensor([1, 1, 1], dtype=torch.int32).cuda(),
+                                  torch.tensor([1, 2, 3], dtype=torch.int32).cuda())
+    moa_b200.check_device_status()
+    ref = orc.prefill_attention_fp32(q.cpu(), k.cpu(), v.cpu(), sm, [1, 1, 1], [1, 2, 3])
+    _close(out, ref, "strided")
+
+
+def test_bf16_fp32_store_meets_the_tolerance_and_bf16_store_is_its_rounding():
+    gen = torch.Generator().manual_seed(12)
+    B, H, N = 1, 3, 700
+    q, k, v = (torch.randn(B, H, N, 128, generator=gen).bfloat16() for _ in range(3))
+    sm = 128 ** -0.5
+    sink_b, local_b = [1, 1, 1], [2, 4, 11]
+    ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b)
+    out32 = _run(q, k, v, sm, sink_b, local_b, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    # P is rounded to bf16 (8 bits) before P.V, so the fp32-store result is checked at a
+    # proportionally wider bound than fp16's 2e-3 / 1e-3
+    _close(out32, ref, "bf16 inputs, fp32 store", 8e-3, 4e-3)
+    out16 = _run(q, k, v, sm, sink_b, local_b)
+    assert out16.dtype == torch.bfloat16
+    assert torch.equal(out16.cpu(), out32.cpu().bfloat16())
+
+
+def test_config0_full_size():
+    """BASELINE config 0: B1 H32 N2048 D128 fp16, 64 sinks, span alpha+beta*N per head."""
+    rng = np.random.RandomState(0)
+    H, N = 32, 2048
+    plan = {"alphas": [[float(rng.choice([128, 256, 512, 1024])) for _ in range(H)]],
+            "betas": [[float(rng.uniform(0, 0.5)) for _ in range(H)]]}
+    cfg = moa_b200.moa_config_to_cache_config(plan, N, 0, verbose=False)
+    caps, static = cfg["cache_size"][0], cfg["static_size"][0]
+    gen = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, H, N, 128, generator=gen).half().cuda() for _ in range(3))
+    sink = torch.tensor(static, dtype=torch.int64).cuda()
+    local = torch.tensor([c - s for c, s in zip(caps, static)], dtype=torch.int64).cuda()
+    out = moa_b200.mixture_of_sparse_attention(q, k, v, 128 ** -0.5, sink_size=sink, local_size=local)
+    moa_b200.check_device_status()
+    ref = orc.prefill_attention_fp32(q.cpu(), k.cpu(), v.cpu(), 128 ** -0.5, [s // 64 for s in static],
+                                     [(c - s) // 64 for c, s in zip(caps, static)])
+    _close(out, ref, "config 0")
+
+
+def test_long_sequence_spot_rows():
+    """N = 16384: rows from the start, the middle and the end are checked against the oracle."""
+    gen = torch.Generator().manual_seed(21)
+    B, H, N = 1, 4, 16384
+    q, k, v = (torch.randn(B, H, N, 128, generator=gen).half() for _ in range(3))
+    sm = 128 ** -0.5
+    sink_b, local_b = [1, 1, 1, 1], [8, 33, 64, 250]
+    out = _run(q, k, v, sm, sink_b, local_b)
+    for a, b in [(0, 256), (8000, 8256), (N - 256, N)]:
+        ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b, row_range=(a, b))
+        _close(out[:, a:b], ref, f"rows {a}:{b}")
+
+
+def test_constant_value_property_full_length():
+    """V constant per dim => output equals it for every row, whatever the mask keeps (N = 65536)."""
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    B, H, N = 1, 2, 65536
+    q = torch.randn(B, H, N, 128, generator=gen, device="cuda").bfloat16()
+    k = torch.randn(B, H, N, 128, generator=gen, device="cuda").bfloat16()
+    const = torch.linspace(-1, 1, 128, device="cuda").bfloat16()
+    v = const[None, None, None, :].expand(B, H, N, 128).contiguous()
+    out = moa_b200.sparse_prefill(q, k, v, 128 ** -0.5, torch.tensor([1, 1], dtype=torch.int32).cuda(),
+                                  torch.tensor([16, 64], dtype=torch.int32).cuda(), out_dtype=torch.float32)
+    moa_b200.check_device_status()
+    assert (out - const.float()[None, None, None]).abs().max() < 5e-3
+
+
+def test_short_prompt_without_sizes_is_dense_causal():
+    gen = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(1, 2, 40, 128, generator=gen).half() for _ in range(3))
+    out = moa_b200.mixture_of_sparse_attention(q.cuda(), k.cuda(), v.cuda(), 0.1)
+    moa_b200.check_device_status()
+    ref = orc.prefill_attention_fp32(q, k, v, 0.1, [0, 0], [1, 1])
+    _close(out, ref, "dense causal N=40")
