@@ -10,8 +10,8 @@ caches filled from a 16k-token random sequence, then decode steps with one new t
 sequence.  A "step" is one fused decode launch (ring append + flash-decoding + bookkeeping)
 over one batch.  `value` is decode tokens/s with the step inputs resident in HBM; `e2e` is the
 same loop through the public API with the step's q/k/v coming from pinned host memory and
-the step's output copied back.  The K/V working set (445 MB) is larger than L2 (126 MB), so no
-L2 flush is needed between steps.
+the step's output copied back.  The K/V working set (about 0.55 GB at the default seed) is larger
+than L2 (126 MB), so no L2 flush is needed between steps.
 
 With N > 1 (torchrun) every rank owns the ring caches of one 32-head shard (heads, or equally
 layers' caches, sharded; no collective on the data path), so per-GPU work is fixed ("weak").
@@ -177,13 +177,13 @@ def run_reference(args):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-def build_cache(caps, device, seed):
+def build_cache(caps, device, seed, fill_tokens):
     import moa_b200
 
     gen = torch.Generator(device=device).manual_seed(seed)
     cache = moa_b200.StaticCircularCache([caps], B, D, [[SINK] * H], device, torch.float16)
-    k = torch.randn(B, H, PREFILL_TOKENS, D, generator=gen, device=device, dtype=torch.float16)
-    v = torch.randn(B, H, PREFILL_TOKENS, D, generator=gen, device=device, dtype=torch.float16)
+    k = torch.randn(B, H, fill_tokens, D, generator=gen, device=device, dtype=torch.float16)
+    v = torch.randn(B, H, fill_tokens, D, generator=gen, device=device, dtype=torch.float16)
     cache.update(k, v, 0)
     torch.cuda.synchronize(device)
     del k, v
@@ -267,7 +267,7 @@ def run_gpu(args):
 
     seed = 1000 + rank
     caps = config1_caps(1000)       # same capacities on every rank; data differs by rank
-    cache, gen = build_cache(caps, device, seed)
+    cache, gen = build_cache(caps, device, seed, args.fill_tokens)
     sm = D ** -0.5
     n_pool = 8
     pool = [tuple(torch.randn(B, H, 1, D, generator=gen, device=device, dtype=torch.float16) for _ in range(3))
@@ -315,9 +315,10 @@ def run_gpu(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "config1: one-layer MoA decode, B16 H32 D128 fp16, caps 64+W_h, W_h in {256..4096}, "
                                    "caches filled from a 16k-token random sequence; fused append + flash-decoding",
-                       "batch": B, "heads_per_gpu": H, "head_dim": D, "kv_slots_per_row": sum(caps),
+                       "batch": B, "fill_tokens": args.fill_tokens, "heads_per_gpu": H, "head_dim": D, "kv_slots_per_row": sum(caps),
                        "parallelism": f"head/cache shards x{world}, one 32-head shard per GPU, no collective",
-                       "l2": "K/V working set 445 MB per step exceeds the 126 MB L2; no flush needed",
+                       "l2": f"K/V working set {moa_b200.decode_bytes(B, caps, D, 2) / 1e6:.0f} MB per step exceeds the "
+                             "126 MB L2; no flush between steps",
                        "seed": 1000},
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 3 * B * H * D * 2, "d2h_bytes_per_step": B * H * D * 2},
@@ -345,9 +346,13 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="moa_b200", choices=["moa_b200", "reference"])
+    ap.add_argument("--batch", type=int, default=16, help="batch size (16 = config 1; smaller only for profiler captures)")
+    ap.add_argument("--fill-tokens", type=int, default=PREFILL_TOKENS, help="tokens the caches are filled from")
     ap.add_argument("--no-prefill", action="store_true", help="skip the informational prefill leg")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    global B
+    B = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:
