@@ -78,6 +78,29 @@ int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_ne
                    void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * moa_decode_fwd_static: moa_decode_fwd without the workspace argument.  It has no counterpart
+ * in the reference; it exists for hosts that cannot allocate device memory on the decode path
+ * (a server whose KV-cache pool already owns all free HBM, a plugin that must not trigger
+ * cudaMalloc's device-wide synchronisation, an FFI binding with no allocator).  The scratch is
+ * a fixed device array of MOA_DECODE_STATIC_SCRATCH_BYTES inside the library, held by every
+ * GPU that loads it until the process exits.  The call allocates nothing.
+ *   - Shapes whose scratch need (moa_decode_workspace_bytes) exceeds the array are refused
+ *     with MOA_ERR_TOO_LARGE; config 1 (B16 H32 D128, 67k slots per row) needs 4.7 MB.
+ *   - The first call on each device looks up the array's device address (once, with that device
+ *     current); make that first call before any stream capture.
+ *   - All calls on a device share the one array: calls that can overlap on the GPU (different
+ *     streams, or concurrent host threads) race on it.  Serialise them or use moa_decode_fwd.
+ * Arguments and semantics otherwise as moa_decode_fwd.
+ * ------------------------------------------------------------------------------------------ */
+#define MOA_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                          void* out, int64_t out_batch_stride, int64_t out_head_stride,
+                          const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                          int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                          int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                          int chunk, moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Ring-cache bookkeeping (StaticCircularCache.update, MoA/attention/cache_utils.py:953-1164).
  *
  * moa_cache_append: decode branch (:1020-1058) without attention.  k_new/v_new (B,H,D) with

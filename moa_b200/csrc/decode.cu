@@ -11,6 +11,8 @@
 //
 // Memory traffic per step is the algorithmic minimum (every valid K and V row once) plus
 // (D+4)*4 bytes of partials per (head, chunk).
+#include <stdio.h>
+
 #include "common.cuh"
 
 namespace moa {
@@ -331,3 +333,76 @@ int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_ne
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Decode entry point that brings its own scratch (no workspace argument, no allocation).
+//
+// Some hosts of this library cannot hand the decode step a workspace: an inference server that has
+// already given every free byte of HBM to its KV-cache pool, a plugin running inside someone else's
+// step loop where cudaMalloc (and the device-wide synchronisation it implies) is not acceptable,
+// or a thin FFI binding without an allocator of its own.  For them the tickets and split partials
+// live in the fixed device array below, which every GPU that loads the library holds until the
+// process exits.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace moa {
+namespace {
+
+static __device__ __align__(256) unsigned char g_decode_scratch[MOA_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_decode_scratch_addr[kMaxDevices];  // device address of g_decode_scratch, per device ordinal
+std::mutex g_decode_scratch_mutex;
+
+// In host code `g_decode_scratch` is only a handle for the symbol, not an address a kernel can use;
+// the address on the current device comes from cudaGetSymbolAddress.  Looked up once per device.
+int decode_static_scratch(void** ptr) {
+  int dev = -1;
+  MOA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error_text("decode_static: device ordinal out of range");
+    return MOA_ERR_INVALID_ARG;
+  }
+  std::lock_guard<std::mutex> lock(g_decode_scratch_mutex);
+  if (g_decode_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    MOA_CUDA_CHECK(cudaGetSymbolAddress(&p, g_decode_scratch));
+    g_decode_scratch_addr[dev] = p;
+  }
+  *ptr = g_decode_scratch_addr[dev];
+  return MOA_OK;
+}
+
+}  // namespace
+}  // namespace moa
+
+extern "C" int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache, const void* k_new,
+                                     const void* v_new, void* out, int64_t out_batch_stride,
+                                     int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
+                                     int64_t* update_index, int64_t* mask_cache, const int64_t* static_size,
+                                     int64_t kv_len, int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                                     int chunk, moa_stream_t stream) {
+  using namespace moa;
+  MOA_REQUIRE(B > 0 && H > 0 && D > 0 && S > 0, "decode_static: bad shape");
+  if (chunk <= 0) chunk = kDefaultChunk;
+  const WsLayout w = ws_layout(B, H, D, S, chunk);
+  if (w.total > (int64_t)MOA_DECODE_STATIC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "decode_static: this shape needs %lld bytes of scratch, the built-in array holds %lld; "
+             "use moa_decode_fwd with a caller-provided workspace",
+             (long long)w.total, (long long)MOA_DECODE_STATIC_SCRATCH_BYTES);
+    set_error_text(msg);
+    return MOA_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  const int rc = decode_static_scratch(&scratch);
+  if (rc != MOA_OK) return rc;
+  // The array keeps whatever the previous call left; the tickets must start at zero.
+  MOA_CUDA_CHECK(cudaMemsetAsync(scratch, 0, (size_t)w.ticket_bytes, (cudaStream_t)stream));
+  return decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
+                                    head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H, D,
+                                    S, sm_scale, dtype, scratch, MOA_DECODE_STATIC_SCRATCH_BYTES, chunk,
+                                    (cudaStream_t)stream);
+}
