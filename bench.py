@@ -212,13 +212,14 @@ def time_region(fn, steps, device, dist):
     return ms, (w0, w1)
 
 
-def prefill_leg(device, peaks_tf, which):
-    """One layer of config 3: B1 H32 N65536 D128 bf16, alpha in {512..4096}, beta in [0, 0.3)."""
+def prefill_leg(device, peaks_tf, which, N=65536):
+    """One layer of config 3: B1 H32 N65536 D128 bf16, alpha in {512..4096}, beta in [0, 0.3).
+    (A smaller N is only for profiler captures.)"""
     import moa_b200
 
     try:
         rng = np.random.RandomState(3000)
-        Hp, N = 32, 65536
+        Hp = 32
         plan = {"alphas": [[float(rng.choice([512, 1024, 2048, 4096])) for _ in range(Hp)]],
                 "betas": [[float(rng.uniform(0, 0.3)) for _ in range(Hp)]]}
         cfg = moa_b200.moa_config_to_cache_config(plan, N, 0, verbose=False)
@@ -239,7 +240,7 @@ def prefill_leg(device, peaks_tf, which):
         moa_b200.check_device_status(device)
         flops = moa_b200.prefill_flops(1, N, D, sink_b, local_b)
         tf = flops / (ms / iters * 1e-3) / 1e12
-        return {"workload": "config3 one layer: block-sparse prefill B1 H32 N65536 D128 bf16",
+        return {"workload": f"config3 one layer: block-sparse prefill B1 H32 N{N} D128 bf16",
                 "tflops_band_dense_equiv": tf, "ms_per_layer": ms / iters, "flop_per_layer": flops,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks_tf, "unit": "TFLOP/s",
                              "frac": tf / peaks_tf, "peak_source": which, "traffic": None}}
@@ -265,6 +266,10 @@ def run_gpu(args):
         dist_mod.init_process_group("nccl", device_id=device)
         dist = dist_mod
 
+    if args.leg == "prefill":
+        hbm_peak, tf_peak, which = measured_peaks()
+        print(json.dumps({"prefill": prefill_leg(device, tf_peak, which, args.prefill_n)}), flush=True)
+        return
     seed = 1000 + rank
     caps = config1_caps(1000)       # same capacities on every rank; data differs by rank
     cache, gen = build_cache(caps, device, seed, args.fill_tokens)
@@ -299,7 +304,7 @@ def run_gpu(args):
     ms_e2e, win2 = time_region(step_e2e, args.steps, device, dist)
 
     hbm_peak, tf_peak, which = measured_peaks()
-    prefill = prefill_leg(device, tf_peak, which) if (world == 1 and not args.no_prefill) else None
+    prefill = prefill_leg(device, tf_peak, which, args.prefill_n) if (world == 1 and not args.no_prefill) else None
     if dist is not None:
         dist.barrier()
     clocks = sampler.stop([win1, win2]) if sampler else None
@@ -348,6 +353,8 @@ def main():
     ap.add_argument("--impl", default="moa_b200", choices=["moa_b200", "reference"])
     ap.add_argument("--batch", type=int, default=16, help="batch size (16 = config 1; smaller only for profiler captures)")
     ap.add_argument("--fill-tokens", type=int, default=PREFILL_TOKENS, help="tokens the caches are filled from")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill"], help="'prefill' runs only the prefill leg")
+    ap.add_argument("--prefill-n", type=int, default=65536, help="sequence length of the prefill leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the informational prefill leg")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
