@@ -9,6 +9,7 @@ int64 temporaries, and ``decode_attention`` fuses the append with flash-decoding
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -85,6 +86,8 @@ class StaticCircularCache:
         self._max_cap = [max(c) for c in cache_size]
         self._static_host = [list(s) for s in static_size]
         self._cap_host = [list(c) for c in cache_size]
+        #: rows of the flattened cache per thread block of the decode kernel (0 = library default)
+        self.decode_chunk = int(os.environ.get("MOA_B200_DECODE_CHUNK", "0"))
         self._workspace: Dict[Any, Tensor] = {}
         self._scan_buffers: Dict[Any, Tuple[Tensor, Tensor]] = {}
 
@@ -142,7 +145,7 @@ class StaticCircularCache:
         key = torch.device(device)
         ws = self._workspace.get(key)
         if ws is None:
-            need = max(lib.moa_decode_workspace_bytes(self.batch_size, h, self.head_dim, s, 0)
+            need = max(lib.moa_decode_workspace_bytes(self.batch_size, h, self.head_dim, s, self.decode_chunk)
                        for h, s in zip(self.num_head_for_each_layer, self.layer_cache_size))
             ws = torch.zeros(need, dtype=torch.uint8, device=key)
             self._workspace[key] = ws
@@ -269,7 +272,8 @@ class StaticCircularCache:
                 self.cache_head_start_index[layer_idx].data_ptr(), self.cache_valid_length[layer_idx].data_ptr(),
                 self.cache_update_index[layer_idx].data_ptr(), self.mask_cache[layer_idx].data_ptr(),
                 self.static_cache_size[layer_idx].data_ptr(), self._kv_len[layer_idx], B, H, D, S, float(sm_scale),
-                _lib.dtype_code(self.dtype), ws.data_ptr(), ws.numel(), 0, _lib.current_stream(device)))
+                _lib.dtype_code(self.dtype), ws.data_ptr(), ws.numel(), self.decode_chunk,
+                _lib.current_stream(device)))
         self._kv_len[layer_idx] += 1
         return out
 

@@ -21,7 +21,18 @@ namespace {
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTileIters = 8;  // 16-byte loads of K (and of V) in flight per thread
-constexpr int kDefaultChunk = 128;
+constexpr int kMinChunk = 128, kMaxChunk = 1024;
+
+// Rows per block when the caller passes chunk = 0.  A block pays a fixed latency chain (metadata,
+// partial write, ticket) whatever it streams, so chunks should be as long as the problem allows
+// while still giving every SM about two rounds of four resident blocks (148 SMs): the smallest
+// power of two >= B*S / (148*4*2), kept within [128, 1024].  Config 1 (B16, S=67k) gets 1024.
+inline int auto_chunk(int B, int64_t S) {
+  const int64_t want = (int64_t)B * S / (148 * 4 * 2);
+  int chunk = kMinChunk;
+  while (chunk < want && chunk < kMaxChunk) chunk *= 2;
+  return chunk;
+}
 
 struct DecodeParams {
   const void* q;
@@ -283,7 +294,7 @@ int decode_launch_with_scratch(const void* q, void* k_cache, void* v_cache, cons
   MOA_REQUIRE((k_new == nullptr) == (v_new == nullptr), "decode: k_new and v_new must both be given or both be NULL");
   MOA_REQUIRE(B > 0 && H > 0 && S > 0 && B <= 65535, "decode: bad shape");
   if (k_new) MOA_REQUIRE(update_index && static_size, "decode: fused append needs update_index and static_size");
-  if (chunk <= 0) chunk = kDefaultChunk;
+  if (chunk <= 0) chunk = auto_chunk(B, S);
   const WsLayout w = ws_layout(B, H, D, S, chunk);
   if (!workspace || workspace_bytes < w.total) {
     set_error_text("decode: workspace missing or smaller than moa_decode_workspace_bytes()");
@@ -311,7 +322,7 @@ extern "C" {
 
 int64_t moa_decode_workspace_bytes(int B, int H, int D, int64_t S, int chunk) {
   if (B <= 0 || H <= 0 || D <= 0 || S <= 0) return 0;
-  if (chunk <= 0) chunk = moa::kDefaultChunk;
+  if (chunk <= 0) chunk = moa::auto_chunk(B, S);
   return moa::ws_layout(B, H, D, S, chunk).total;
 }
 
@@ -385,7 +396,7 @@ extern "C" int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache
                                      int chunk, moa_stream_t stream) {
   using namespace moa;
   MOA_REQUIRE(B > 0 && H > 0 && D > 0 && S > 0, "decode_static: bad shape");
-  if (chunk <= 0) chunk = kDefaultChunk;
+  if (chunk <= 0) chunk = auto_chunk(B, S);
   const WsLayout w = ws_layout(B, H, D, S, chunk);
   if (w.total > (int64_t)MOA_DECODE_STATIC_SCRATCH_BYTES) {
     char msg[256];
