@@ -1,15 +1,21 @@
 // Block-sparse causal prefill (attention sink + per-head sliding window) on tcgen05 / TMEM / TMA.
 //
-// One thread block computes one 128-row query tile of one (batch, head).  Roles:
-//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r); reads S from TMEM, writes
-//              P (fp16/bf16) to shared memory in the 128-byte-swizzled K-major layout, keeps the
-//              running max / sum, rescales O in TMEM when the max moved, runs the epilogue
-//   warp  4    TMA producer (one lane): Q once, then K/V tiles of 64 tokens through a ring of
-//              kStages shared-memory stages
-//   warp  5    MMA issuer (one lane) and owner of the TMEM allocation:
-//              S_j = Q K_j^T (M128 N64 K128) into one of two S buffers, O += P_j V_j (M128 N128 K64)
-// Only the 64-token KV blocks inside "sink U band" of the tile are ever loaded; blocks outside
-// are skipped, and only the (at most three) edge blocks of a tile get an element mask.
+// One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
+// A and B that share every K/V tile brought into shared memory.  Roles:
+//   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
+//              tile (= TMEM lane r); reads S from TMEM, writes P (fp16/bf16, two per 32-bit
+//              column) back over the same TMEM columns, keeps the running max / sum, rescales O
+//              in TMEM when the max moved, runs the epilogue
+//   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
+//              two rings of shared-memory stages (K is released after S = QK^T, V after O += PV)
+//   warp  9    MMA issuer (one lane) and owner of the TMEM allocation:
+//              S = Q K^T (M128 N64 K128, both operands from shared memory) into one of two S
+//              buffers per tile, O += P V (M128 N128 K64, P from TMEM, V from shared memory as an
+//              MN-major operand)
+// While one tile's softmax runs, the tensor core works on the other tile (and on the next S of the
+// same tile), so exponentials and MMAs overlap.  Only the 64-token KV blocks inside "sink U band"
+// of the super-tile are loaded; a tile skips the blocks only the other tile sees, and only the (at
+// most three) edge blocks of a tile get an element mask.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -28,40 +34,61 @@ namespace moa {
 namespace {
 
 constexpr int kD = 128;            // head_dim this kernel is built for
-constexpr int kBM = 128;           // query rows per tile
+constexpr int kBM = 128;           // query rows per tile (two tiles per block)
 constexpr int kBN = 64;            // KV tokens per tile (= the mask's block size)
-constexpr int kStages = 4;         // K/V ring depth
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;  // O: [0,128)  S0: [128,192)  S1: [192,256)
-constexpr uint32_t kColO = 0, kColS = 128;
+constexpr int kKStages = 4;        // K ring depth
+constexpr int kVStages = 4;        // V ring depth
+constexpr int kSoftmaxThreads = 128;  // per tile
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;
+// TMEM columns: O_A [0,128) O_B [128,256); S/P buffers of 64 columns: A0 256, A1 320, B0 384, B1 448
+__host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
+__host__ __device__ constexpr uint32_t col_s(int x, int buf) { return 256u + (uint32_t)x * 128u + (uint32_t)buf * 64u; }
 
-constexpr int kQBytes = kBM * kD * 2;       // 32 KiB  (two 16 KiB halves: dims 0-63, 64-127)
+constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per tile (two 16 KiB halves: dims 0-63, 64-127)
 constexpr int kKBytes = kBN * kD * 2;       // 16 KiB  (two 8 KiB halves)
-constexpr int kStageBytes = 2 * kKBytes;    // K then V
-constexpr int kPBytes = kBM * kBN * 2;      // 16 KiB
 constexpr int kSmemQ = 0;
-constexpr int kSmemKV = kSmemQ + kQBytes;
-constexpr int kSmemP = kSmemKV + kStages * kStageBytes;
-constexpr int kSmemCtl = kSmemP + 2 * kPBytes;
-constexpr int kSmemBytes = kSmemCtl + 256 + 1024;  // control block + slack for 1024-byte alignment
+constexpr int kSmemK = kSmemQ + 2 * kQBytes;
+constexpr int kSmemV = kSmemK + kKStages * kKBytes;
+constexpr int kSmemCtl = kSmemV + kVStages * kKBytes;
+constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
 
 // status codes written to status[0] when a wait gives up
-enum { kWaitQ = 1, kWaitKVFull = 2, kWaitKVEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7 };
+enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
+       kWaitVFull = 8, kWaitVEmpty = 9 };
 
 struct Ctl {
   uint64_t q_full;
-  uint64_t kv_full[kStages];
-  uint64_t kv_empty[kStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t pv_done;
-  uint64_t o_full;
+  uint64_t k_full[kKStages];
+  uint64_t k_empty[kKStages];
+  uint64_t v_full[kVStages];
+  uint64_t v_empty[kVStages];
+  uint64_t s_full[2][2];   // [tile][buffer]
+  uint64_t p_full[2][2];
+  uint64_t pv_done[2];
+  uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
 };
+static_assert(sizeof(Ctl) <= 512, "control block");
+
+// Optional phase timing for kernel development (never compiled into the library): with
+// -DMOA_PREFILL_PROFILE, selected threads add clock64 deltas into status[16 + slot].
+#ifdef MOA_PREFILL_PROFILE
+#define PROF_DECL long long _pt = clock64();
+#define PROF_ADD(slot, cond)                                                        \
+  do {                                                                              \
+    long long _now = clock64();                                                     \
+    if (cond) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), \
+                        (unsigned long long)(_now - _pt));                          \
+    _pt = _now;                                                                     \
+  } while (0)
+#else
+#define PROF_DECL
+#define PROF_ADD(slot, cond)
+#endif
 
 struct PrefillParams {
   void* out;
@@ -104,8 +131,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait.  Returns false when the block is aborting (this wait or another one gave up).
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -123,6 +149,10 @@ __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* ctl,
     }
   }
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, ctl, status, code);
+}
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2, int c3) {
@@ -134,7 +164,6 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -149,6 +178,17 @@ __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc]   (A: 128 lanes x K, two 16-bit values per 32-bit column)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -201,19 +241,24 @@ __host__ __device__ constexpr uint32_t make_idesc(int is_bf16, int b_mn_major, i
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// KV blocks a query tile visits: [0, nA) (sink part) then [bB, bB + nB) (band part).
+// KV blocks a query super-tile visits: [0, nA) (sink part) then [bB, bB + nB) (band part).
 struct TileBlocks {
   int nA, bB, nB;
   __device__ __forceinline__ int count() const { return nA + nB; }
   __device__ __forceinline__ int block(int i) const { return i < nA ? i : bB + (i - nA); }
 };
-__device__ __forceinline__ TileBlocks tile_blocks(int t, int nb, int sink_b, int local_b) {
-  const int hi = min(2 * t + 2, nb);                 // blocks [0, hi) are at or below the diagonal
+// t_lo, t_hi: first and last 128-row tile of the super-tile
+__device__ __forceinline__ TileBlocks tile_blocks(int t_lo, int t_hi, int nb, int sink_b, int local_b) {
+  const int hi = min(2 * t_hi + 2, nb);              // blocks [0, hi) are at or below the diagonal
   TileBlocks r;
   r.nA = max(0, min(sink_b, hi));
-  r.bB = max(r.nA, 2 * t + 1 - local_b);              // first band block of the upper half
+  r.bB = max(r.nA, 2 * t_lo + 1 - local_b);           // first band block of the first 64 rows
   r.nB = max(0, hi - r.bB);
   return r;
+}
+// does 128-row tile t (if it exists) take part in KV block j?
+__device__ __forceinline__ bool tile_sees(bool exists, int t, int j, int nb, int sink_b, int local_b) {
+  return exists && j < min(2 * t + 2, nb) && (j < sink_b || j >= 2 * t + 1 - local_b);
 }
 
 template <typename T, bool OUT_F32>
@@ -225,31 +270,39 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemCtl);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int ntiles = (int)((p.N + kBM - 1) / kBM);
-  const int t = ntiles - 1 - (int)blockIdx.x;  // heaviest tiles are scheduled first
+  const int nsuper = (int)((p.N + 2 * kBM - 1) / (2 * kBM));
+  const int st = nsuper - 1 - (int)blockIdx.x;  // heaviest super-tiles are scheduled first
   const int h = blockIdx.y, b = blockIdx.z;
   const int nb = (int)((p.N + kBN - 1) / kBN);
   const int sink_b = p.sink_blocks[h], local_b = p.local_blocks[h];
-  const TileBlocks tb = tile_blocks(t, nb, sink_b, local_b);
-  const int ntile_kv = tb.count();
+  const int t0 = 2 * st, t1 = 2 * st + 1;
+  const bool active1 = (int64_t)t1 * kBM < p.N;      // the second tile exists
+  const TileBlocks tb = tile_blocks(t0, active1 ? t1 : t0, nb, sink_b, local_b);
+  const int nkv = tb.count();
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&ctl->kv_full[s], 1);
-      mbar_init(&ctl->kv_empty[s], 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(&ctl->k_full[s], 1);
+      mbar_init(&ctl->k_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&ctl->s_full[s], 1);
-      mbar_init(&ctl->p_full[s], kSoftmaxThreads);
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(&ctl->v_full[s], 1);
+      mbar_init(&ctl->v_empty[s], 1);
     }
-    mbar_init(&ctl->pv_done, 1);
-    mbar_init(&ctl->o_full, 1);
+    for (int x = 0; x < 2; ++x) {
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(&ctl->s_full[x][s], 1);
+        mbar_init(&ctl->p_full[x][s], kSoftmaxThreads);
+      }
+      mbar_init(&ctl->pv_done[x], 1);
+      mbar_init(&ctl->o_full[x], 1);
+    }
     ctl->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
@@ -260,135 +313,179 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem = *(volatile uint32_t*)&ctl->tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctl->q_full, kQBytes);
-      tma_load_4d(smem + kSmemQ, &map_q, &ctl->q_full, 0, t * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes / 2, &map_q, &ctl->q_full, 64, t * kBM, h, b);
-      int issued = 0;
-      for (int j = 0; j < ntile_kv; ++j) {
-        const int s = j % kStages;
-        if (!mbar_wait(&ctl->kv_empty[s], ((j / kStages) & 1) ^ 1, ctl, p.status, kWaitKVEmpty)) break;
-        uint8_t* st = smem + kSmemKV + s * kStageBytes;
-        const int row = tb.block(j) * kBN;
-        mbar_expect_tx(&ctl->kv_full[s], kStageBytes);
-        tma_load_4d(st, &map_k, &ctl->kv_full[s], 0, row, h, b);
-        tma_load_4d(st + kKBytes / 2, &map_k, &ctl->kv_full[s], 64, row, h, b);
-        tma_load_4d(st + kKBytes, &map_v, &ctl->kv_full[s], 0, row, h, b);
-        tma_load_4d(st + kKBytes + kKBytes / 2, &map_v, &ctl->kv_full[s], 64, row, h, b);
-        issued = j + 1;
+      mbar_expect_tx(&ctl->q_full, 2 * kQBytes);
+      tma_load_4d(smem + kSmemQ, &map_q, &ctl->q_full, 0, t0 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes / 2, &map_q, &ctl->q_full, 64, t0 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes, &map_q, &ctl->q_full, 0, t1 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes + kQBytes / 2, &map_q, &ctl->q_full, 64, t1 * kBM, h, b);
+      int k_issued = 0, v_issued = 0;
+      // V lags K by one tile: it is needed one MMA step later
+      for (int u = 0; u <= nkv; ++u) {
+        if (u < nkv) {
+          const int s = u % kKStages;
+          if (!mbar_wait(&ctl->k_empty[s], ((u / kKStages) & 1) ^ 1, ctl, p.status, kWaitKEmpty)) break;
+          uint8_t* dst = smem + kSmemK + s * kKBytes;
+          const int row = tb.block(u) * kBN;
+          mbar_expect_tx(&ctl->k_full[s], kKBytes);
+          tma_load_4d(dst, &map_k, &ctl->k_full[s], 0, row, h, b);
+          tma_load_4d(dst + kKBytes / 2, &map_k, &ctl->k_full[s], 64, row, h, b);
+          k_issued = u + 1;
+        }
+        if (u >= 1) {
+          const int uv = u - 1, s = uv % kVStages;
+          if (!mbar_wait(&ctl->v_empty[s], ((uv / kVStages) & 1) ^ 1, ctl, p.status, kWaitVEmpty)) break;
+          uint8_t* dst = smem + kSmemV + s * kKBytes;
+          const int row = tb.block(uv) * kBN;
+          mbar_expect_tx(&ctl->v_full[s], kKBytes);
+          tma_load_4d(dst, &map_v, &ctl->v_full[s], 0, row, h, b);
+          tma_load_4d(dst + kKBytes / 2, &map_v, &ctl->v_full[s], 64, row, h, b);
+          v_issued = uv + 1;
+        }
       }
       if (*(volatile int*)&ctl->abort) {
         // drain: shared memory must not be released while bulk copies into it are in flight
-        const uint64_t t0 = globaltimer_ns();
-        for (int j = max(0, issued - kStages); j < issued; ++j) {
-          while (!mbar_try_wait(&ctl->kv_full[j % kStages], (j / kStages) & 1) &&
-                 globaltimer_ns() - t0 < kWaitLimitNs) {
+        const uint64_t tstart = globaltimer_ns();
+        for (int u = max(0, k_issued - kKStages); u < k_issued; ++u) {
+          while (!mbar_try_wait(&ctl->k_full[u % kKStages], (u / kKStages) & 1) &&
+                 globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        while (!mbar_try_wait(&ctl->q_full, 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
+        for (int u = max(0, v_issued - kVStages); u < v_issued; ++u) {
+          while (!mbar_try_wait(&ctl->v_full[u % kVStages], (u / kVStages) & 1) &&
+                 globaltimer_ns() - tstart < kWaitLimitNs) {
+          }
+        }
+        while (!mbar_try_wait(&ctl->q_full, 0) && globaltimer_ns() - tstart < kWaitLimitNs) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, kD);
-      const uint32_t q_addr = smem_u32(smem + kSmemQ);
+      // descriptors differ only in their start-address field (bytes >> 4): build each base once
+      const uint64_t q_desc[2] = {make_desc(smem_u32(smem + kSmemQ), 16, 1024),
+                                  make_desc(smem_u32(smem + kSmemQ + kQBytes), 16, 1024)};
+      const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
+      const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
       bool ok = mbar_wait(&ctl->q_full, 0, ctl, p.status, kWaitQ);
       tc_fence_after();
+      int qk_count[2] = {0, 0};  // S tiles issued per query tile
+      int pv_count[2] = {0, 0};  // PV steps issued per query tile
+      PROF_DECL
 
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % kStages;
-        if (!mbar_wait(&ctl->kv_full[s], (j / kStages) & 1, ctl, p.status, kWaitKVFull)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + kSmemKV + s * kStageBytes);
-        const uint32_t d_tmem = tmem + kColS + (uint32_t)(j & 1) * kBN;
+      for (int u = 0; ok && u <= nkv; ++u) {
+        if (u < nkv) {
+          const int s = u % kKStages, j = tb.block(u);
+          if (!mbar_wait(&ctl->k_full[s], (u / kKStages) & 1, ctl, p.status, kWaitKFull)) { ok = false; break; }
+          PROF_ADD(10, true);
+          tc_fence_after();
+          const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-          const uint64_t a = make_desc(q_addr + half * (kQBytes / 2) + off, 16, 1024);
-          const uint64_t bd = make_desc(k_addr + half * (kKBytes / 2) + off, 16, 1024);
-          tc_mma_ss(d_tmem, a, bd, idesc_qk, kk > 0);
-        }
-        tc_commit(&ctl->s_full[j & 1]);
-        return true;
-      };
-
-      if (ok && ntile_kv > 0) ok = issue_qk(0);
-      if (ok && ntile_kv > 1) ok = issue_qk(1);
-      for (int j = 0; ok && j < ntile_kv; ++j) {
-        if (!mbar_wait(&ctl->p_full[j & 1], (j >> 1) & 1, ctl, p.status, kWaitP)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int s = j % kStages;
-        const uint32_t v_addr = smem_u32(smem + kSmemKV + s * kStageBytes + kKBytes);
-        const uint32_t p_addr = smem_u32(smem + kSmemP + (j & 1) * kPBytes);
+          for (int x = 0; x < 2; ++x) {
+            if (!tile_sees(x == 0 || active1, t0 + x, j, nb, sink_b, local_b)) continue;
+            const int i = qk_count[x]++;
+            const uint32_t d_tmem = tmem + col_s(x, i & 1);
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          const uint64_t a = make_desc(p_addr + kk * 32, 16, 1024);
-          // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
-          const uint64_t bd = make_desc(v_addr + kk * 2048, kKBytes / 2, 1024);
-          tc_mma_ss(tmem + kColO, a, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kD / 16; ++kk) {
+              // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
+              const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+              const uint64_t a = q_desc[x] + (uint64_t)((half * (kQBytes / 2) + off) >> 4);
+              const uint64_t bd = k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4);
+              tc_mma_ss(d_tmem, a, bd, idesc_qk, kk > 0);
+            }
+            tc_commit(&ctl->s_full[x][i & 1]);
+          }
+          tc_commit(&ctl->k_empty[s]);
+          PROF_ADD(11, true);
         }
-        tc_commit(&ctl->kv_empty[s]);
-        tc_commit(&ctl->pv_done);
-        if (j + 2 < ntile_kv) ok = issue_qk(j + 2);
+        if (u >= 1) {
+          const int uv = u - 1, s = uv % kVStages, j = tb.block(uv);
+          if (!mbar_wait(&ctl->v_full[s], (uv / kVStages) & 1, ctl, p.status, kWaitVFull)) { ok = false; break; }
+          PROF_ADD(12, true);
+          const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (!tile_sees(x == 0 || active1, t0 + x, j, nb, sink_b, local_b)) continue;
+            const int i = pv_count[x]++;
+            if (!mbar_wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitP)) { ok = false; break; }
+            PROF_ADD(13 + x, true);
+            tc_fence_after();
+            const uint32_t p_tmem = tmem + col_s(x, i & 1);  // P overlays the first 32 columns of its S buffer
+#pragma unroll
+            for (int kk = 0; kk < kBN / 16; ++kk) {
+              // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
+              tc_mma_ts(tmem + col_o(x), p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                        (i > 0 || kk > 0) ? 1u : 0u);
+            }
+            tc_commit(&ctl->pv_done[x]);
+            PROF_ADD(15, true);
+          }
+          if (!ok) break;
+          tc_commit(&ctl->v_empty[s]);
+        }
       }
-      if (ok) tc_commit(&ctl->o_full);
+      if (ok) {
+        tc_commit(&ctl->o_full[0]);
+        tc_commit(&ctl->o_full[1]);
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    const int row = tid;                                  // tile row == TMEM lane
-    const int64_t i_tok = (int64_t)t * kBM + row;         // query position
+    const int x = warp >> 2;                              // which query tile this warpgroup owns
+    const int tq = t0 + x;
+    const bool tile_active = (x == 0) || active1;
+    const int row = tid & 127;                            // tile row == TMEM lane
+    const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
     const int bi = (int)(i_tok >> 6);
     const int lo_band = bi + 1 - local_b;                 // first band block this row sees
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    uint8_t* p_row_base = smem + kSmemP + row * 128;
-    const int sw = row & 7;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
     float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
     float l = 0.f;
     bool ok = true;
+    int i = 0;                 // KV blocks this tile has taken part in
+    PROF_DECL
+    const bool prof_me = (tid & 127) == 0;
 
-    for (int j = 0; j < ntile_kv; ++j) {
-      ok = mbar_wait(&ctl->s_full[j & 1], (j >> 1) & 1, ctl, p.status, kWaitS);
+    for (int u = 0; tile_active && u < nkv; ++u) {
+      const int jb = tb.block(u);
+      if (!tile_sees(tile_active, tq, jb, nb, sink_b, local_b)) continue;
+      ok = mbar_wait(&ctl->s_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      PROF_ADD(0, prof_me);
       tc_fence_after();
+      const uint32_t s_addr = lane_base + col_s(x, i & 1);
       uint32_t sv[64];
       {
         uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
         uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
-        tmem_ld32(lane_base + kColS + (uint32_t)(j & 1) * kBN, lo32);
-        tmem_ld32(lane_base + kColS + (uint32_t)(j & 1) * kBN + 32, hi32);
+        tmem_ld32(s_addr, lo32);
+        tmem_ld32(s_addr + 32, hi32);
         tmem_wait_ld();
       }
-      const int jb = tb.block(j);
-      const bool edge = (jb >= 2 * t) || (jb >= sink_b && jb == 2 * t + 1 - local_b);
-      float mt = -INFINITY;
+      PROF_ADD(1, prof_me);
+      const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
+      float mt = -INFINITY;   // row max of the raw scores
       if (edge) {
         const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
         const int64_t j0 = (int64_t)jb * kBN;
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const bool vis = row_sees && (j0 + c <= i_tok) && (j0 + c < p.N);
-          const float x = vis ? __uint_as_float(sv[c]) * p.scale_log2 : -INFINITY;
-          sv[c] = __float_as_uint(x);
-          mt = fmaxf(mt, x);
+          if (!vis) sv[c] = 0xff800000u;  // -inf
+          mt = fmaxf(mt, __uint_as_float(sv[c]));
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float x = __uint_as_float(sv[c]) * p.scale_log2;
-          sv[c] = __float_as_uint(x);
-          mt = fmaxf(mt, x);
-        }
+        for (int c = 0; c < 64; ++c) mt = fmaxf(mt, __uint_as_float(sv[c]));
       }
+      mt *= p.scale_log2;     // scale_log2 > 0, so the max commutes with the scaling
       // lazy rescale: move the reference max only when it grew by more than 2^8
       float factor = 1.f;
       if (mt > m_used + 8.f) {
@@ -396,50 +493,49 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         l *= factor;
         m_used = mt;
       }
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = exp2f(__uint_as_float(sv[c]) - m_sub);
-        const float p1 = exp2f(__uint_as_float(sv[c + 1]) - m_sub);
+        const float p0 = exp2f(fmaf(__uint_as_float(sv[c]), p.scale_log2, neg_m));
+        const float p1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, neg_m));
         l += p0 + p1;
         pk[c >> 1] = Cvt<T>::pack(p0, p1);
       }
-      // P row -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c at c ^ (row % 8))
-      uint8_t* prow = p_row_base + (j & 1) * kPBytes;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        *reinterpret_cast<uint4*>(prow + ((c ^ sw) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
-      fence_async_smem();
-      // O may only be touched (and P[j&1] of two tiles ago is only free) once PV of tile j-1 is done
-      if (j > 0) {
-        ok = mbar_wait(&ctl->pv_done, (j - 1) & 1, ctl, p.status, kWaitPV);
+      // P row -> TMEM, over the S columns just read (two values per column, even key in the low half)
+      PROF_ADD(2, prof_me);
+      tmem_st32(s_addr, pk);
+      // O may only be touched once PV of this tile's previous block is done
+      if (i > 0) {
+        ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        PROF_ADD(3, prof_me);
         tc_fence_after();
         if (__any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kD; c0 += 32) {
             uint32_t ov[32];
-            tmem_ld32(lane_base + kColO + c0, ov);
+            tmem_ld32(lane_base + col_o(x) + c0, ov);
             tmem_wait_ld();
 #pragma unroll
             for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-            tmem_st32(lane_base + kColO + c0, ov);
+            tmem_st32(lane_base + col_o(x) + c0, ov);
           }
-          tmem_wait_st();
         }
       }
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&ctl->p_full[j & 1]);
+      mbar_arrive(&ctl->p_full[x][i & 1]);
+      PROF_ADD(4, prof_me);
+      ++i;
     }
 
-    if (ok && ntile_kv > 0) {
-      ok = mbar_wait(&ctl->o_full, 0, ctl, p.status, kWaitO);
+    if (ok && i > 0) {
+      ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && ntile_kv > 0) {
+    if (ok && i > 0) {
       tc_fence_after();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
       const bool store = i_tok < p.N;
@@ -448,7 +544,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll 1
       for (int c0 = 0; c0 < kD; c0 += 32) {
         uint32_t ov[32];
-        tmem_ld32(lane_base + kColO + c0, ov);
+        tmem_ld32(lane_base + col_o(x) + c0, ov);
         tmem_wait_ld();
         if (store) {
           if (OUT_F32) {
@@ -461,12 +557,12 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           } else {
 #pragma unroll
             for (int c = 0; c < 32; c += 8) {
-              uint4 u;
-              u.x = Cvt<T>::pack(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l);
-              u.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
-              u.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
-              u.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = u;
+              uint4 uo;
+              uo.x = Cvt<T>::pack(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l);
+              uo.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
+              uo.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
+              uo.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = uo;
             }
           }
         }
@@ -477,7 +573,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
@@ -548,7 +644,8 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   using namespace moa;
   MOA_REQUIRE(q && k && v && out && sink_blocks && local_blocks && status, "prefill: null pointer");
   MOA_REQUIRE(B > 0 && H > 0 && N > 0 && B <= 65535 && H <= 65535, "prefill: bad shape");
-  MOA_REQUIRE(N < (1LL << 31) - 256, "prefill: sequence too long");
+  MOA_REQUIRE(N < (1LL << 31) - 512, "prefill: sequence too long");
+  MOA_REQUIRE(sm_scale > 0.f, "prefill: sm_scale must be positive");
   if (D != kD) {
     set_error_text("prefill: head_dim must be 128");
     return MOA_ERR_UNSUPPORTED;
@@ -572,8 +669,8 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   p.out = out; p.o_sb = o_sb; p.o_sn = o_sn; p.o_sh = o_sh;
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
-  const int ntiles = (int)((N + kBM - 1) / kBM);
-  dim3 grid((unsigned)ntiles, (unsigned)H, (unsigned)B);
+  const int nsuper = (int)((N + 2 * kBM - 1) / (2 * kBM));
+  dim3 grid((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == MOA_F16) {
     return out_f32 ? launch_prefill<__half, true>(mq, mk, mv, p, grid, st)
