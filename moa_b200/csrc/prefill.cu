@@ -3,19 +3,21 @@
 // One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
 // A and B that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
-//              tile (= TMEM lane r); reads S from TMEM, writes P (fp16/bf16, two per 32-bit
-//              column) back over the same TMEM columns, keeps the running max / sum, rescales O
-//              in TMEM when the max moved, runs the epilogue
-//   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
-//              two rings of shared-memory stages (K is released after S = QK^T, V after O += PV)
+//              tile (= TMEM lane r).  It first copies its Q row from global memory into TMEM (Q is
+//              the A operand of S = Q K^T and stays there), then per KV block reads S from TMEM,
+//              writes P (fp16/bf16, two per 32-bit column) back over the same TMEM columns, keeps
+//              the running max / sum, rescales O in TMEM when the max moved, and runs the epilogue
+//   warp  8    TMA producer (one lane): K and V tiles of 64 tokens through two rings of
+//              shared-memory stages (K is released after S = QK^T, V after O += PV)
 //   warp  9    MMA issuer (one lane) and owner of the TMEM allocation:
-//              S = Q K^T (M128 N64 K128, both operands from shared memory) into one of two S
-//              buffers per tile, O += P V (M128 N128 K64, P from TMEM, V from shared memory as an
-//              MN-major operand)
-// While one tile's softmax runs, the tensor core works on the other tile (and on the next S of the
-// same tile), so exponentials and MMAs overlap.  Only the 64-token KV blocks inside "sink U band"
-// of the super-tile are loaded; a tile skips the blocks only the other tile sees, and only the (at
-// most three) edge blocks of a tile get an element mask.
+//              S = Q K^T (M128 N64 K128) and O += P V (M128 N128 K64).  In both the A operand
+//              (Q, P) comes from TMEM and only the B operand (K, V) from shared memory: with A in
+//              shared memory an M128 N64 step would need 6 KB of operands per 32 cycles, more
+//              than shared memory delivers.
+// The two tiles alternate on the tensor core: while one tile's softmax runs, the other tile's
+// P.V and next Q.K^T execute.  Only the 64-token KV blocks inside "sink U band" of the super-tile
+// are loaded; a tile skips the blocks only the other tile sees, and only the (at most three) edge
+// blocks of a tile get an element mask.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -36,19 +38,19 @@ namespace {
 constexpr int kD = 128;            // head_dim this kernel is built for
 constexpr int kBM = 128;           // query rows per tile (two tiles per block)
 constexpr int kBN = 64;            // KV tokens per tile (= the mask's block size)
-constexpr int kKStages = 4;        // K ring depth
-constexpr int kVStages = 4;        // V ring depth
+constexpr int kKStages = 5;        // K ring depth
+constexpr int kVStages = 5;        // V ring depth
 constexpr int kSoftmaxThreads = 128;  // per tile
 constexpr int kThreads = 320;
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns: O_A [0,128) O_B [128,256); S/P buffers of 64 columns: A0 256, A1 320, B0 384, B1 448
-__host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
-__host__ __device__ constexpr uint32_t col_s(int x, int buf) { return 256u + (uint32_t)x * 128u + (uint32_t)buf * 64u; }
+// TMEM columns: Q_A [0,64) Q_B [64,128) (two dims per column), O_A [128,256) O_B [256,384),
+// S_A [384,448) S_B [448,512); P overlays the first 32 columns of its tile's S
+__host__ __device__ constexpr uint32_t col_q(int x) { return (uint32_t)x * 64u; }
+__host__ __device__ constexpr uint32_t col_o(int x) { return 128u + (uint32_t)x * 128u; }
+__host__ __device__ constexpr uint32_t col_s(int x) { return 384u + (uint32_t)x * 64u; }
 
-constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per tile (two 16 KiB halves: dims 0-63, 64-127)
-constexpr int kKBytes = kBN * kD * 2;       // 16 KiB  (two 8 KiB halves)
-constexpr int kSmemQ = 0;
-constexpr int kSmemK = kSmemQ + 2 * kQBytes;
+constexpr int kKBytes = kBN * kD * 2;       // 16 KiB per K or V tile (two 8 KiB halves: dims 0-63, 64-127)
+constexpr int kSmemK = 0;
 constexpr int kSmemV = kSmemK + kKStages * kKBytes;
 constexpr int kSmemCtl = kSmemV + kVStages * kKBytes;
 constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
@@ -56,18 +58,17 @@ constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
 
 // status codes written to status[0] when a wait gives up
-enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
+enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitO = 7,
        kWaitVFull = 8, kWaitVEmpty = 9 };
 
 struct Ctl {
-  uint64_t q_full;
   uint64_t k_full[kKStages];
   uint64_t k_empty[kKStages];
   uint64_t v_full[kVStages];
   uint64_t v_empty[kVStages];
-  uint64_t s_full[2][2];   // [tile][buffer]
-  uint64_t p_full[2][2];
-  uint64_t pv_done[2];
+  uint64_t q_ready[2];  // [tile]: Q rows are in TMEM
+  uint64_t s_full[2];   // [tile]: S written by the tensor core
+  uint64_t p_full[2];   // [tile]: P (and a rescaled O) written by the softmax threads
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
@@ -77,20 +78,28 @@ static_assert(sizeof(Ctl) <= 512, "control block");
 // Optional phase timing for kernel development (never compiled into the library): with
 // -DMOA_PREFILL_PROFILE, selected threads add clock64 deltas into status[16 + slot].
 #ifdef MOA_PREFILL_PROFILE
-#define PROF_DECL long long _pt = clock64();
-#define PROF_ADD(slot, cond)                                                        \
-  do {                                                                              \
-    long long _now = clock64();                                                     \
-    if (cond) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (slot), \
-                        (unsigned long long)(_now - _pt));                          \
-    _pt = _now;                                                                     \
+#define PROF_DECL long long _pt = clock64(); long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const int _pbase = 0;
+#define PROF_ADD(slot, cond)                     \
+  do {                                           \
+    long long _now = clock64();                  \
+    _pa[(slot) % 8 + 0 * _pbase] += _now - _pt;  \
+    _pt = _now;                                  \
+  } while (0)
+#define PROF_FLUSH(base, cond)                                                                        \
+  do {                                                                                                \
+    if (cond)                                                                                         \
+      for (int _i = 0; _i < 8; ++_i)                                                                  \
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (base) + _i, (unsigned long long)_pa[_i]); \
   } while (0)
 #else
 #define PROF_DECL
 #define PROF_ADD(slot, cond)
+#define PROF_FLUSH(base, cond)
 #endif
 
 struct PrefillParams {
+  const void* q;
+  int64_t q_sb, q_sh, q_sn;
   void* out;
   int64_t o_sb, o_sn, o_sh;
   const int32_t* sink_blocks;
@@ -168,17 +177,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 
 // D[tmem] (+)= A[tmem] * B[smem desc]   (A: 128 lanes x K, two 16-bit values per 32-bit column)
@@ -263,8 +261,8 @@ __device__ __forceinline__ bool tile_sees(bool exists, int t, int j, int nb, int
 
 template <typename T, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
-moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemCtl);
@@ -282,7 +280,6 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
 
   if (tid == 0) {
-    mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kKStages; ++s) {
       mbar_init(&ctl->k_full[s], 1);
       mbar_init(&ctl->k_empty[s], 1);
@@ -292,11 +289,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&ctl->v_empty[s], 1);
     }
     for (int x = 0; x < 2; ++x) {
-      for (int s = 0; s < 2; ++s) {
-        mbar_init(&ctl->s_full[x][s], 1);
-        mbar_init(&ctl->p_full[x][s], kSoftmaxThreads);
-      }
-      mbar_init(&ctl->pv_done[x], 1);
+      mbar_init(&ctl->q_ready[x], kSoftmaxThreads);
+      mbar_init(&ctl->s_full[x], 1);
+      mbar_init(&ctl->p_full[x], kSoftmaxThreads);
       mbar_init(&ctl->o_full[x], 1);
     }
     ctl->abort = 0;
@@ -316,11 +311,6 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctl->q_full, 2 * kQBytes);
-      tma_load_4d(smem + kSmemQ, &map_q, &ctl->q_full, 0, t0 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes / 2, &map_q, &ctl->q_full, 64, t0 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes, &map_q, &ctl->q_full, 0, t1 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes + kQBytes / 2, &map_q, &ctl->q_full, 64, t1 * kBM, h, b);
       int k_issued = 0, v_issued = 0;
       // V lags K by one tile: it is needed one MMA step later
       for (int u = 0; u <= nkv; ++u) {
@@ -358,8 +348,6 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        while (!mbar_try_wait(&ctl->q_full, 0) && globaltimer_ns() - tstart < kWaitLimitNs) {
-        }
       }
     }
   } else if (warp == 9) {
@@ -368,71 +356,92 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, kD);
       // descriptors differ only in their start-address field (bytes >> 4): build each base once
-      const uint64_t q_desc[2] = {make_desc(smem_u32(smem + kSmemQ), 16, 1024),
-                                  make_desc(smem_u32(smem + kSmemQ + kQBytes), 16, 1024)};
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
-      bool ok = mbar_wait(&ctl->q_full, 0, ctl, p.status, kWaitQ);
-      tc_fence_after();
-      int qk_count[2] = {0, 0};  // S tiles issued per query tile
-      int pv_count[2] = {0, 0};  // PV steps issued per query tile
+      bool ok = true;
+      int n_qk[2] = {0, 0};  // S tiles issued per query tile
+      int n_pv[2] = {0, 0};  // P.V steps issued per query tile
       PROF_DECL
 
-      for (int u = 0; ok && u <= nkv; ++u) {
-        if (u < nkv) {
-          const int s = u % kKStages, j = tb.block(u);
-          if (!mbar_wait(&ctl->k_full[s], (u / kKStages) & 1, ctl, p.status, kWaitKFull)) { ok = false; break; }
-          PROF_ADD(10, true);
-          tc_fence_after();
-          const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
+      // S_x = Q_x K_u^T for KV entry u of the visit list (K stage already waited for)
+      auto issue_qk = [&](int x, int u) {
+        const uint64_t k_desc = k_desc0 + (uint64_t)((u % kKStages) * (kKBytes >> 4));
 #pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            if (!tile_sees(x == 0 || active1, t0 + x, j, nb, sink_b, local_b)) continue;
-            const int i = qk_count[x]++;
-            const uint32_t d_tmem = tmem + col_s(x, i & 1);
-#pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk) {
-              // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
-              const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-              const uint64_t a = q_desc[x] + (uint64_t)((half * (kQBytes / 2) + off) >> 4);
-              const uint64_t bd = k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4);
-              tc_mma_ss(d_tmem, a, bd, idesc_qk, kk > 0);
-            }
-            tc_commit(&ctl->s_full[x][i & 1]);
-          }
-          tc_commit(&ctl->k_empty[s]);
-          PROF_ADD(11, true);
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          // 16 dims per step: 8 TMEM columns of Q; in K 32 B inside the swizzle row, dims 64-127 in the second half-tile
+          const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+          tc_mma_ts(tmem + col_s(x), tmem + col_q(x) + kk * 8, k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4),
+                    idesc_qk, kk > 0);
         }
-        if (u >= 1) {
-          const int uv = u - 1, s = uv % kVStages, j = tb.block(uv);
-          if (!mbar_wait(&ctl->v_full[s], (uv / kVStages) & 1, ctl, p.status, kWaitVFull)) { ok = false; break; }
-          PROF_ADD(12, true);
-          const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            if (!tile_sees(x == 0 || active1, t0 + x, j, nb, sink_b, local_b)) continue;
-            const int i = pv_count[x]++;
-            if (!mbar_wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitP)) { ok = false; break; }
-            PROF_ADD(13 + x, true);
+        tc_commit(&ctl->s_full[x]);
+        ++n_qk[x];
+      };
+
+      for (int x = 0; ok && x < 2; ++x) {
+        if (x == 1 && !active1) break;
+        ok = mbar_wait(&ctl->q_ready[x], 0, ctl, p.status, kWaitQ);
+      }
+      if (ok && nkv > 0) {
+        ok = mbar_wait(&ctl->k_full[0], 0, ctl, p.status, kWaitKFull);
+        tc_fence_after();
+        if (ok) {
+          for (int x = 0; x < 2; ++x)
+            if (tile_sees(x == 0 || active1, t0 + x, tb.block(0), nb, sink_b, local_b)) issue_qk(x, 0);
+          tc_commit(&ctl->k_empty[0]);
+        }
+      }
+      PROF_ADD(10, true);
+      for (int u = 0; ok && u < nkv; ++u) {
+        const int j = tb.block(u);
+        const bool has_next = u + 1 < nkv;
+        const int jn = has_next ? tb.block(u + 1) : 0;
+        bool v_waited = false, k_waited = false;
+        for (int x = 0; ok && x < 2; ++x) {
+          const bool exists = (x == 0) || active1;
+          if (tile_sees(exists, t0 + x, j, nb, sink_b, local_b)) {
+            // O_x += P_x V_u once the softmax threads have written P_x
+            if (!v_waited) {
+              ok = mbar_wait(&ctl->v_full[u % kVStages], (u / kVStages) & 1, ctl, p.status, kWaitVFull);
+              v_waited = true;
+              if (!ok) break;
+            }
+            PROF_ADD(11, true);
+            ok = mbar_wait(&ctl->p_full[x], n_pv[x] & 1, ctl, p.status, kWaitP);
+            if (!ok) break;
+            PROF_ADD(12 + x, true);
             tc_fence_after();
-            const uint32_t p_tmem = tmem + col_s(x, i & 1);  // P overlays the first 32 columns of its S buffer
+            const uint64_t v_desc = v_desc0 + (uint64_t)((u % kVStages) * (kKBytes >> 4));
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk) {
               // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
-              tc_mma_ts(tmem + col_o(x), p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                        (i > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_ts(tmem + col_o(x), tmem + col_s(x) + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                        (n_pv[x] > 0 || kk > 0) ? 1u : 0u);
             }
-            tc_commit(&ctl->pv_done[x]);
-            PROF_ADD(15, true);
+            ++n_pv[x];
+            PROF_ADD(14, true);
           }
-          if (!ok) break;
-          tc_commit(&ctl->v_empty[s]);
+          if (has_next && tile_sees(exists, t0 + x, jn, nb, sink_b, local_b)) {
+            // the tile's S columns are free again (its P.V above, or an earlier one, is queued ahead)
+            if (!k_waited) {
+              ok = mbar_wait(&ctl->k_full[(u + 1) % kKStages], ((u + 1) / kKStages) & 1, ctl, p.status, kWaitKFull);
+              k_waited = true;
+              if (!ok) break;
+              tc_fence_after();
+            }
+            PROF_ADD(15, true);
+            issue_qk(x, u + 1);
+            PROF_ADD(16, true);
+          }
         }
+        if (!ok) break;
+        tc_commit(&ctl->v_empty[u % kVStages]);
+        if (has_next) tc_commit(&ctl->k_empty[(u + 1) % kKStages]);
       }
       if (ok) {
         tc_commit(&ctl->o_full[0]);
         tc_commit(&ctl->o_full[1]);
       }
+      PROF_FLUSH(10, true);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
@@ -445,22 +454,43 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int lo_band = bi + 1 - local_b;                 // first band block this row sees
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
+    if (tile_active) {
+      // Q row -> TMEM: a 32-bit word of the row already holds dims (2c, 2c+1) as the A operand wants
+      const uint4* qrow = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb +
+                                                         (int64_t)h * p.q_sh + i_tok * p.q_sn);
+      const bool in_range = i_tok < p.N;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t qv[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 u4 = in_range ? __ldg(qrow + half * 8 + c) : make_uint4(0, 0, 0, 0);
+          qv[4 * c] = u4.x; qv[4 * c + 1] = u4.y; qv[4 * c + 2] = u4.z; qv[4 * c + 3] = u4.w;
+        }
+        tmem_st32(lane_base + col_q(x) + half * 32, qv);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&ctl->q_ready[x]);
+    }
+
     float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
     float l = 0.f;
     bool ok = true;
     int i = 0;                 // KV blocks this tile has taken part in
     PROF_DECL
     const bool prof_me = (tid & 127) == 0;
+    (void)prof_me;
 
     for (int u = 0; tile_active && u < nkv; ++u) {
       const int jb = tb.block(u);
       if (!tile_sees(tile_active, tq, jb, nb, sink_b, local_b)) continue;
-      ok = mbar_wait(&ctl->s_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitS);
+      ok = mbar_wait(&ctl->s_full[x], i & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       PROF_ADD(0, prof_me);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + col_s(x, i & 1);
+      const uint32_t s_addr = lane_base + col_s(x);
       uint32_t sv[64];
       {
         uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
@@ -471,7 +501,6 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       PROF_ADD(1, prof_me);
       const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
-      float mt = -INFINITY;   // row max of the raw scores
       if (edge) {
         const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
         const int64_t j0 = (int64_t)jb * kBN;
@@ -479,58 +508,63 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int c = 0; c < 64; ++c) {
           const bool vis = row_sees && (j0 + c <= i_tok) && (j0 + c < p.N);
           if (!vis) sv[c] = 0xff800000u;  // -inf
-          mt = fmaxf(mt, __uint_as_float(sv[c]));
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) mt = fmaxf(mt, __uint_as_float(sv[c]));
       }
-      mt *= p.scale_log2;     // scale_log2 > 0, so the max commutes with the scaling
+      // row max of the raw scores, four independent chains
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) mx[r] = fmaxf(mx[r], __uint_as_float(sv[c + r]));
+      }
+      // scale_log2 > 0, so the max commutes with the scaling
+      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       // lazy rescale: move the reference max only when it grew by more than 2^8
       float factor = 1.f;
       if (mt > m_used + 8.f) {
         factor = (m_used == -INFINITY) ? 1.f : exp2f(m_used - mt);
-        l *= factor;
         m_used = mt;
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       uint32_t pk[32];
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#ifdef MOA_PREFILL_NOEXP   // development probe: how fast is everything except the exponentials?
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) pk[c >> 1] = sv[c] & 0x3c003c00u;
+      ls[0] = neg_m;
+#else
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float p0 = exp2f(fmaf(__uint_as_float(sv[c]), p.scale_log2, neg_m));
         const float p1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, neg_m));
-        l += p0 + p1;
+        ls[(c >> 1) & 3] += p0 + p1;
         pk[c >> 1] = Cvt<T>::pack(p0, p1);
       }
-      // P row -> TMEM, over the S columns just read (two values per column, even key in the low half)
+#endif
+      l = fmaf(l, factor, (ls[0] + ls[1]) + (ls[2] + ls[3]));
       PROF_ADD(2, prof_me);
+      // P row -> TMEM, over the S columns just read (two values per column, even key in the low half)
       tmem_st32(s_addr, pk);
-      // O may only be touched once PV of this tile's previous block is done
-      if (i > 0) {
-        ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        PROF_ADD(3, prof_me);
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, factor != 1.f)) {
+      // S of this block is complete, so the tile's previous P.V (queued before it) is too: O may be touched
+      if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kD; c0 += 32) {
-            uint32_t ov[32];
-            tmem_ld32(lane_base + col_o(x) + c0, ov);
-            tmem_wait_ld();
+        for (int c0 = 0; c0 < kD; c0 += 32) {
+          uint32_t ov[32];
+          tmem_ld32(lane_base + col_o(x) + c0, ov);
+          tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-            tmem_st32(lane_base + col_o(x) + c0, ov);
-          }
+          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+          tmem_st32(lane_base + col_o(x) + c0, ov);
         }
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&ctl->p_full[x][i & 1]);
-      PROF_ADD(4, prof_me);
+      mbar_arrive(&ctl->p_full[x]);
+      PROF_ADD(3, prof_me);
       ++i;
     }
 
+    PROF_FLUSH(0, prof_me);
     if (ok && i > 0) {
       ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
@@ -620,15 +654,15 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_
 }
 
 template <typename T, bool F32>
-int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
-                   dim3 grid, cudaStream_t stream) {
+int launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
+                   cudaStream_t stream) {
   auto kern = moa_prefill_kernel<T, F32>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     MOA_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured = true;
   }
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(mk, mv, p);
   MOA_CUDA_CHECK(cudaGetLastError());
   return MOA_OK;
 }
@@ -660,12 +694,12 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
                   ((uintptr_t)out % 16 == 0),
               "prefill: pointers must be 16-byte aligned");
   MOA_REQUIRE(o_sb % 8 == 0 && o_sn % 8 == 0 && o_sh % 8 == 0, "prefill: out strides must be multiples of 8 elements");
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mk, mv;
   int rc;
-  if ((rc = make_map(&mq, q, dtype, B, H, N, q_sb, q_sh, q_sn, kBM)) != MOA_OK) return rc;
   if ((rc = make_map(&mk, k, dtype, B, H, N, k_sb, k_sh, k_sn, kBN)) != MOA_OK) return rc;
   if ((rc = make_map(&mv, v, dtype, B, H, N, v_sb, v_sh, v_sn, kBN)) != MOA_OK) return rc;
   PrefillParams p;
+  p.q = q; p.q_sb = q_sb; p.q_sh = q_sh; p.q_sn = q_sn;
   p.out = out; p.o_sb = o_sb; p.o_sn = o_sn; p.o_sh = o_sh;
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
@@ -673,9 +707,9 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   dim3 grid((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == MOA_F16) {
-    return out_f32 ? launch_prefill<__half, true>(mq, mk, mv, p, grid, st)
-                   : launch_prefill<__half, false>(mq, mk, mv, p, grid, st);
+    return out_f32 ? launch_prefill<__half, true>(mk, mv, p, grid, st)
+                   : launch_prefill<__half, false>(mk, mv, p, grid, st);
   }
-  return out_f32 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, grid, st)
-                 : launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, grid, st);
+  return out_f32 ? launch_prefill<__nv_bfloat16, true>(mk, mv, p, grid, st)
+                 : launch_prefill<__nv_bfloat16, false>(mk, mv, p, grid, st);
 }
