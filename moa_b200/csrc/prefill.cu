@@ -3,21 +3,25 @@
 // One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
 // A and B that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
-//              tile (= TMEM lane r).  It first copies its Q row from global memory into TMEM (Q is
-//              the A operand of S = Q K^T and stays there), then per KV block reads S from TMEM,
-//              writes P (fp16/bf16, two per 32-bit column) back over the same TMEM columns, keeps
-//              the running max / sum, rescales O in TMEM when the max moved, and runs the epilogue
-//   warp  8    TMA producer (one lane): K and V tiles of 64 tokens through two rings of
-//              shared-memory stages (K is released after S = QK^T, V after O += PV)
-//   warp  9    MMA issuer (one lane) and owner of the TMEM allocation:
-//              S = Q K^T (M128 N64 K128) and O += P V (M128 N128 K64).  In both the A operand
-//              (Q, P) comes from TMEM and only the B operand (K, V) from shared memory: with A in
-//              shared memory an M128 N64 step would need 6 KB of operands per 32 cycles, more
-//              than shared memory delivers.
-// The two tiles alternate on the tensor core: while one tile's softmax runs, the other tile's
-// P.V and next Q.K^T execute.  Only the 64-token KV blocks inside "sink U band" of the super-tile
-// are loaded; a tile skips the blocks only the other tile sees, and only the (at most three) edge
-// blocks of a tile get an element mask.
+//              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM and at once hands
+//              the S columns back (so the tensor core can start the tile's next S), computes the
+//              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
+//              column) to the tile's P columns in TMEM, rescales O in TMEM when the max moved,
+//              and finally runs the epilogue
+//   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
+//              two rings of shared-memory stages
+//   warp  9,10 MMA issuers of tile A and tile B (one lane each; warp 9 owns the TMEM allocation):
+//              S = Q K^T (M128 N64 K128, Q and K from shared memory), O += P V (M128 N128 K64,
+//              P from TMEM, V from shared memory as an MN-major operand).  An issuer is a single
+//              thread that competes for issue slots with the softmax warps of its scheduler, so
+//              its loop is kept to a few dozen instructions per step: the KV blocks a tile takes
+//              part in are two index ranges in closed form, and ring stages are handed back with
+//              plain mbarrier arrives wherever completion is already known.
+// Per tile the order is S(i) -> [softmax loads S(i)] -> S(i+1) may start -> [softmax writes P(i)]
+// -> O += P(i) V(i): the next S is computed while the exponentials of the current one run, and
+// the two tiles interleave on the tensor core.  Only the 64-token KV blocks inside "sink U band"
+// of the super-tile are loaded; a tile skips the blocks only the other tile sees, and only the
+// (at most three) edge blocks of a tile get an element mask.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -38,57 +42,63 @@ namespace {
 constexpr int kD = 128;            // head_dim this kernel is built for
 constexpr int kBM = 128;           // query rows per tile (two tiles per block)
 constexpr int kBN = 64;            // KV tokens per tile (= the mask's block size)
-constexpr int kKStages = 5;        // K ring depth
-constexpr int kVStages = 5;        // V ring depth
+constexpr int kStages = 4;         // depth of the K ring and of the V ring (power of two)
 constexpr int kSoftmaxThreads = 128;  // per tile
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns: Q_A [0,64) Q_B [64,128) (two dims per column), O_A [128,256) O_B [256,384),
-// S_A [384,448) S_B [448,512); P overlays the first 32 columns of its tile's S
-__host__ __device__ constexpr uint32_t col_q(int x) { return (uint32_t)x * 64u; }
-__host__ __device__ constexpr uint32_t col_o(int x) { return 128u + (uint32_t)x * 128u; }
-__host__ __device__ constexpr uint32_t col_s(int x) { return 384u + (uint32_t)x * 64u; }
+// TMEM columns: O_A [0,128) O_B [128,256), S_A [256,320) S_B [320,384), P_A [384,416) P_B [416,448)
+__host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
+__host__ __device__ constexpr uint32_t col_s(int x) { return 256u + (uint32_t)x * 64u; }
+__host__ __device__ constexpr uint32_t col_p(int x) { return 384u + (uint32_t)x * 32u; }
 
-constexpr int kKBytes = kBN * kD * 2;       // 16 KiB per K or V tile (two 8 KiB halves: dims 0-63, 64-127)
-constexpr int kSmemK = 0;
-constexpr int kSmemV = kSmemK + kKStages * kKBytes;
-constexpr int kSmemCtl = kSmemV + kVStages * kKBytes;
+constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per Q tile (two 16 KiB halves: dims 0-63, 64-127)
+constexpr int kKBytes = kBN * kD * 2;       // 16 KiB per K or V tile (two 8 KiB halves)
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kSmemQ + 2 * kQBytes;
+constexpr int kSmemV = kSmemK + kStages * kKBytes;
+constexpr int kSmemCtl = kSmemV + kStages * kKBytes;
 constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock: far above any legitimate wait
+constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drain loops of the abort path
 
 // status codes written to status[0] when a wait gives up
-enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitO = 7,
-       kWaitVFull = 8, kWaitVEmpty = 9 };
+enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
+       kWaitVFull = 8, kWaitVEmpty = 9, kWaitSFree = 10 };
 
 struct Ctl {
-  uint64_t k_full[kKStages];
-  uint64_t k_empty[kKStages];
-  uint64_t v_full[kVStages];
-  uint64_t v_empty[kVStages];
-  uint64_t q_ready[2];  // [tile]: Q rows are in TMEM
-  uint64_t s_full[2];   // [tile]: S written by the tensor core
-  uint64_t p_full[2];   // [tile]: P (and a rescaled O) written by the softmax threads
+  uint64_t q_full;
+  uint64_t k_full[kStages];
+  uint64_t v_full[kStages];
+  uint64_t k_empty[2][kStages];  // [tile]: that tile is done with the K stage
+  uint64_t v_empty[2][kStages];
+  uint64_t s_full[2];   // [tile] tensor core -> softmax: S is in TMEM
+  uint64_t s_free[2];   // [tile] softmax -> issuer: S has been read, its columns may be overwritten
+  uint64_t p_full[2];   // [tile] softmax -> issuer: P is in TMEM (and O rescaled)
+  uint64_t pv_done[2];  // [tile] tensor core -> softmax: O += P V finished (P columns free, O may be touched)
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
 
-// Optional phase timing for kernel development (never compiled into the library): with
-// -DMOA_PREFILL_PROFILE, selected threads add clock64 deltas into status[16 + slot].
+// Development probes (never compiled into the library): MOA_PREFILL_DBG bit 1 skips the softmax
+// threads' TMEM traffic, bit 2 skips the MMAs themselves (barrier handshakes only).
+#ifndef MOA_PREFILL_DBG
+#define MOA_PREFILL_DBG 0
+#endif
 #ifdef MOA_PREFILL_PROFILE
-#define PROF_DECL long long _pt = clock64(); long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const int _pbase = 0;
+#define PROF_DECL long long _pt = clock64(); long long _pa[16] = {0}; const int _pbase = 0;
 #define PROF_ADD(slot, cond)                     \
   do {                                           \
     long long _now = clock64();                  \
-    _pa[(slot) % 8 + 0 * _pbase] += _now - _pt;  \
+    _pa[(slot) % 16 + 0 * _pbase] += _now - _pt;  \
     _pt = _now;                                  \
   } while (0)
 #define PROF_FLUSH(base, cond)                                                                        \
   do {                                                                                                \
     if (cond)                                                                                         \
-      for (int _i = 0; _i < 8; ++_i)                                                                  \
+      for (int _i = 0; _i < 16; ++_i)                                                                 \
         atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (base) + _i, (unsigned long long)_pa[_i]); \
   } while (0)
 #else
@@ -98,8 +108,6 @@ static_assert(sizeof(Ctl) <= 512, "control block");
 #endif
 
 struct PrefillParams {
-  const void* q;
-  int64_t q_sb, q_sh, q_sn;
   void* out;
   int64_t o_sb, o_sn, o_sh;
   const int32_t* sink_blocks;
@@ -140,13 +148,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait.  Returns false when the block is aborting (this wait or another one gave up).
+// The limit is counted with clock64 (a cheap per-SM counter); reading %globaltimer costs far more
+// than a typical wait lasts and must stay off this path.
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 0) {
+    if ((spin & 255u) == 0) {
       if (*(volatile int*)&ctl->abort) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         *(volatile int*)&ctl->abort = 1;
         if (atomicCAS(&status[0], 0, code) == 0) {
           status[1] = (int32_t)blockIdx.x;
@@ -177,6 +187,17 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // D[tmem] (+)= A[tmem] * B[smem desc]   (A: 128 lanes x K, two 16-bit values per 32-bit column)
@@ -239,11 +260,12 @@ __host__ __device__ constexpr uint32_t make_idesc(int is_bf16, int b_mn_major, i
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// KV blocks a query super-tile visits: [0, nA) (sink part) then [bB, bB + nB) (band part).
+// KV blocks a query super-tile visits, as a list: entries [0, nA) are blocks 0..nA-1 (sink part),
+// entries [nA, nA + nB) are blocks bB, bB+1, ... (band part).
 struct TileBlocks {
   int nA, bB, nB;
   __device__ __forceinline__ int count() const { return nA + nB; }
-  __device__ __forceinline__ int block(int i) const { return i < nA ? i : bB + (i - nA); }
+  __device__ __forceinline__ int block(int u) const { return u < nA ? u : bB + (u - nA); }
 };
 // t_lo, t_hi: first and last 128-row tile of the super-tile
 __device__ __forceinline__ TileBlocks tile_blocks(int t_lo, int t_hi, int nb, int sink_b, int local_b) {
@@ -254,15 +276,27 @@ __device__ __forceinline__ TileBlocks tile_blocks(int t_lo, int t_hi, int nb, in
   r.nB = max(0, hi - r.bB);
   return r;
 }
-// does 128-row tile t (if it exists) take part in KV block j?
-__device__ __forceinline__ bool tile_sees(bool exists, int t, int j, int nb, int sink_b, int local_b) {
-  return exists && j < min(2 * t + 2, nb) && (j < sink_b || j >= 2 * t + 1 - local_b);
+// The list entries one 128-row tile t takes part in: [0, s_end) and [b_begin, b_end).
+// (Block j is visible to the tile iff j < min(2t+2, nb) and (j < sink or j >= 2t+1-local).)
+struct TileSeen {
+  int s_end, b_begin, b_end, total;
+  __device__ __forceinline__ int entry(int i) const { return i < s_end ? i : b_begin + (i - s_end); }
+};
+__device__ __forceinline__ TileSeen tile_seen(bool exists, int t, const TileBlocks& tb, int nb, int local_b) {
+  TileSeen r;
+  const int hi = min(2 * t + 2, nb), lo = 2 * t + 1 - local_b;
+  r.s_end = exists ? min(tb.nA, hi) : 0;
+  r.b_begin = tb.nA + max(lo, tb.bB) - tb.bB;
+  r.b_end = tb.nA + min(hi, tb.bB + tb.nB) - tb.bB;
+  if (!exists || tb.nB == 0 || r.b_end < r.b_begin) r.b_end = r.b_begin;
+  r.total = r.s_end + (r.b_end - r.b_begin);
+  return r;
 }
 
 template <typename T, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
-moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                   const PrefillParams p) {
+moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemCtl);
@@ -280,18 +314,20 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
 
   if (tid == 0) {
-    for (int s = 0; s < kKStages; ++s) {
+    mbar_init(&ctl->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl->k_full[s], 1);
-      mbar_init(&ctl->k_empty[s], 1);
-    }
-    for (int s = 0; s < kVStages; ++s) {
       mbar_init(&ctl->v_full[s], 1);
-      mbar_init(&ctl->v_empty[s], 1);
+      for (int x = 0; x < 2; ++x) {
+        mbar_init(&ctl->k_empty[x][s], 1);
+        mbar_init(&ctl->v_empty[x][s], 1);
+      }
     }
     for (int x = 0; x < 2; ++x) {
-      mbar_init(&ctl->q_ready[x], kSoftmaxThreads);
       mbar_init(&ctl->s_full[x], 1);
+      mbar_init(&ctl->s_free[x], kSoftmaxThreads);
       mbar_init(&ctl->p_full[x], kSoftmaxThreads);
+      mbar_init(&ctl->pv_done[x], 1);
       mbar_init(&ctl->o_full[x], 1);
     }
     ctl->abort = 0;
@@ -311,12 +347,22 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      mbar_expect_tx(&ctl->q_full, 2 * kQBytes);
+      tma_load_4d(smem + kSmemQ, &map_q, &ctl->q_full, 0, t0 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes / 2, &map_q, &ctl->q_full, 64, t0 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes, &map_q, &ctl->q_full, 0, t1 * kBM, h, b);
+      tma_load_4d(smem + kSmemQ + kQBytes + kQBytes / 2, &map_q, &ctl->q_full, 64, t1 * kBM, h, b);
       int k_issued = 0, v_issued = 0;
-      // V lags K by one tile: it is needed one MMA step later
-      for (int u = 0; u <= nkv; ++u) {
+      bool ok = true;
+      // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
+      // tiles' issuers have handed it back.
+      for (int u = 0; ok && u <= nkv; ++u) {
         if (u < nkv) {
-          const int s = u % kKStages;
-          if (!mbar_wait(&ctl->k_empty[s], ((u / kKStages) & 1) ^ 1, ctl, p.status, kWaitKEmpty)) break;
+          const int s = u & (kStages - 1);
+          const uint32_t par = ((u / kStages) & 1) ^ 1;
+          ok = mbar_wait(&ctl->k_empty[0][s], par, ctl, p.status, kWaitKEmpty) &&
+               mbar_wait(&ctl->k_empty[1][s], par, ctl, p.status, kWaitKEmpty);
+          if (!ok) break;
           uint8_t* dst = smem + kSmemK + s * kKBytes;
           const int row = tb.block(u) * kBN;
           mbar_expect_tx(&ctl->k_full[s], kKBytes);
@@ -325,8 +371,11 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           k_issued = u + 1;
         }
         if (u >= 1) {
-          const int uv = u - 1, s = uv % kVStages;
-          if (!mbar_wait(&ctl->v_empty[s], ((uv / kVStages) & 1) ^ 1, ctl, p.status, kWaitVEmpty)) break;
+          const int uv = u - 1, s = uv & (kStages - 1);
+          const uint32_t par = ((uv / kStages) & 1) ^ 1;
+          ok = mbar_wait(&ctl->v_empty[0][s], par, ctl, p.status, kWaitVEmpty) &&
+               mbar_wait(&ctl->v_empty[1][s], par, ctl, p.status, kWaitVEmpty);
+          if (!ok) break;
           uint8_t* dst = smem + kSmemV + s * kKBytes;
           const int row = tb.block(uv) * kBN;
           mbar_expect_tx(&ctl->v_full[s], kKBytes);
@@ -338,167 +387,167 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (*(volatile int*)&ctl->abort) {
         // drain: shared memory must not be released while bulk copies into it are in flight
         const uint64_t tstart = globaltimer_ns();
-        for (int u = max(0, k_issued - kKStages); u < k_issued; ++u) {
-          while (!mbar_try_wait(&ctl->k_full[u % kKStages], (u / kKStages) & 1) &&
+        for (int u = max(0, k_issued - kStages); u < k_issued; ++u) {
+          while (!mbar_try_wait(&ctl->k_full[u & (kStages - 1)], (u / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        for (int u = max(0, v_issued - kVStages); u < v_issued; ++u) {
-          while (!mbar_try_wait(&ctl->v_full[u % kVStages], (u / kVStages) & 1) &&
+        for (int u = max(0, v_issued - kStages); u < v_issued; ++u) {
+          while (!mbar_try_wait(&ctl->v_full[u & (kStages - 1)], (u / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
+        }
+        while (!mbar_try_wait(&ctl->q_full, 0) && globaltimer_ns() - tstart < kWaitLimitNs) {
         }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= 9) {
+    // ------------------------------------------------------------------ MMA issuer of tile x
     if (lane == 0) {
+      const int x = warp - 9;
+      const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, kD);
       // descriptors differ only in their start-address field (bytes >> 4): build each base once
+      const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
+      const uint32_t s_tmem = tmem + col_s(x), o_tmem = tmem + col_o(x), p_tmem = tmem + col_p(x);
+      uint64_t* const k_empty = ctl->k_empty[x];
+      uint64_t* const v_empty = ctl->v_empty[x];
       bool ok = true;
-      int n_qk[2] = {0, 0};  // S tiles issued per query tile
-      int n_pv[2] = {0, 0};  // P.V steps issued per query tile
       PROF_DECL
 
-      // S_x = Q_x K_u^T for KV entry u of the visit list (K stage already waited for)
-      auto issue_qk = [&](int x, int u) {
-        const uint64_t k_desc = k_desc0 + (uint64_t)((u % kKStages) * (kKBytes >> 4));
+      // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).
+      // The stage must have been filled first, so that the arrives of successive ring rounds
+      // cannot run ahead of the producer.
+      auto skip_entries = [&](int from, int to) {
+        for (int w = from; ok && w < to; ++w) {
+          const int s = w & (kStages - 1);
+          const uint32_t par = (w / kStages) & 1;
+          ok = mbar_wait(&ctl->k_full[s], par, ctl, p.status, kWaitKFull);
+          if (ok) mbar_arrive(&k_empty[s]);
+          if (ok) ok = mbar_wait(&ctl->v_full[s], par, ctl, p.status, kWaitVFull);
+          if (ok) mbar_arrive(&v_empty[s]);
+        }
+      };
+      // S = Q K^T for list entry u
+      auto issue_qk = [&](int u) {
+        const int s = u & (kStages - 1);
+        ok = mbar_wait(&ctl->k_full[s], (u / kStages) & 1, ctl, p.status, kWaitKFull);
+        if (!ok) return;
+        tc_fence_after();
+        const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
-          // 16 dims per step: 8 TMEM columns of Q; in K 32 B inside the swizzle row, dims 64-127 in the second half-tile
+          // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
           const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-          tc_mma_ts(tmem + col_s(x), tmem + col_q(x) + kk * 8, k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4),
-                    idesc_qk, kk > 0);
+          if (!(MOA_PREFILL_DBG & 4))
+          tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
+                    k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
         }
         tc_commit(&ctl->s_full[x]);
-        ++n_qk[x];
       };
 
-      for (int x = 0; ok && x < 2; ++x) {
-        if (x == 1 && !active1) break;
-        ok = mbar_wait(&ctl->q_ready[x], 0, ctl, p.status, kWaitQ);
+      // skip_entries interleaves the K and V side entry by entry, which is what keeps it free of
+      // deadlock against a producer that fills K(u) and V(u-1) alternately.
+      if (seen.total > 0) {
+        skip_entries(0, seen.entry(0));
+        if (ok) ok = mbar_wait(&ctl->q_full, 0, ctl, p.status, kWaitQ);
+        if (ok) issue_qk(seen.entry(0));
+      } else {
+        skip_entries(0, nkv);
       }
-      if (ok && nkv > 0) {
-        ok = mbar_wait(&ctl->k_full[0], 0, ctl, p.status, kWaitKFull);
-        tc_fence_after();
-        if (ok) {
-          for (int x = 0; x < 2; ++x)
-            if (tile_sees(x == 0 || active1, t0 + x, tb.block(0), nb, sink_b, local_b)) issue_qk(x, 0);
-          tc_commit(&ctl->k_empty[0]);
-        }
-      }
-      PROF_ADD(10, true);
-      for (int u = 0; ok && u < nkv; ++u) {
-        const int j = tb.block(u);
-        const bool has_next = u + 1 < nkv;
-        const int jn = has_next ? tb.block(u + 1) : 0;
-        bool v_waited = false, k_waited = false;
-        for (int x = 0; ok && x < 2; ++x) {
-          const bool exists = (x == 0) || active1;
-          if (tile_sees(exists, t0 + x, j, nb, sink_b, local_b)) {
-            // O_x += P_x V_u once the softmax threads have written P_x
-            if (!v_waited) {
-              ok = mbar_wait(&ctl->v_full[u % kVStages], (u / kVStages) & 1, ctl, p.status, kWaitVFull);
-              v_waited = true;
-              if (!ok) break;
-            }
-            PROF_ADD(11, true);
-            ok = mbar_wait(&ctl->p_full[x], n_pv[x] & 1, ctl, p.status, kWaitP);
-            if (!ok) break;
-            PROF_ADD(12 + x, true);
-            tc_fence_after();
-            const uint64_t v_desc = v_desc0 + (uint64_t)((u % kVStages) * (kKBytes >> 4));
-#pragma unroll
-            for (int kk = 0; kk < kBN / 16; ++kk) {
-              // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
-              tc_mma_ts(tmem + col_o(x), tmem + col_s(x) + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
-                        (n_pv[x] > 0 || kk > 0) ? 1u : 0u);
-            }
-            ++n_pv[x];
-            PROF_ADD(14, true);
-          }
-          if (has_next && tile_sees(exists, t0 + x, jn, nb, sink_b, local_b)) {
-            // the tile's S columns are free again (its P.V above, or an earlier one, is queued ahead)
-            if (!k_waited) {
-              ok = mbar_wait(&ctl->k_full[(u + 1) % kKStages], ((u + 1) / kKStages) & 1, ctl, p.status, kWaitKFull);
-              k_waited = true;
-              if (!ok) break;
-              tc_fence_after();
-            }
-            PROF_ADD(15, true);
-            issue_qk(x, u + 1);
-            PROF_ADD(16, true);
-          }
-        }
+      PROF_ADD(0, true);
+      int u_prev = -1;   // entry whose V stage is still to be handed back
+      for (int i = 0; ok && i < seen.total; ++i) {
+        const int u = seen.entry(i);
+        const bool has_next = i + 1 < seen.total;
+        const int un = has_next ? seen.entry(i + 1) : u + 1;
+        const bool gap = un != u + 1;   // entries between u and un belong to the other tile only (rare)
+        // (1) the softmax threads hold S(i) in registers: K(u) is done with, the next S may start
+        ok = mbar_wait(&ctl->s_free[x], i & 1, ctl, p.status, kWaitSFree);
         if (!ok) break;
-        tc_commit(&ctl->v_empty[u % kVStages]);
-        if (has_next) tc_commit(&ctl->k_empty[(u + 1) % kKStages]);
+        PROF_ADD(1, true);
+        mbar_arrive(&k_empty[u & (kStages - 1)]);
+        if (has_next && !gap) {
+          issue_qk(un);
+          if (!ok) break;
+        }
+        PROF_ADD(2, true);
+        // (2) P(i) is in TMEM; the softmax threads waited for P.V(i-1) before writing it, so V(u_prev) is free
+        ok = mbar_wait(&ctl->p_full[x], i & 1, ctl, p.status, kWaitP);
+        if (!ok) break;
+        PROF_ADD(3, true);
+        if (u_prev >= 0) mbar_arrive(&v_empty[u_prev & (kStages - 1)]);
+        const int s = u & (kStages - 1);
+        ok = mbar_wait(&ctl->v_full[s], (u / kStages) & 1, ctl, p.status, kWaitVFull);
+        if (!ok) break;
+        PROF_ADD(4, true);
+        tc_fence_after();
+        const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
+          if (!(MOA_PREFILL_DBG & 4))
+          tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&ctl->pv_done[x]);
+        PROF_ADD(5, true);
+        u_prev = u;
+        if (has_next && gap) {
+          // hand back V(u) through the tensor core's completion, then the other tile's entries, then go on
+          tc_commit(&v_empty[s]);
+          u_prev = -1;
+          skip_entries(u + 1, un);
+          if (ok) issue_qk(un);
+        }
       }
-      if (ok) {
-        tc_commit(&ctl->o_full[0]);
-        tc_commit(&ctl->o_full[1]);
+      if (ok && seen.total > 0) {
+        tc_commit(&ctl->o_full[x]);
+        if (u_prev >= 0) tc_commit(&v_empty[u_prev & (kStages - 1)]);
+        skip_entries(seen.entry(seen.total - 1) + 1, nkv);
       }
-      PROF_FLUSH(10, true);
+      PROF_FLUSH(16 + 16 * x, true);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = warp >> 2;                              // which query tile this warpgroup owns
     const int tq = t0 + x;
-    const bool tile_active = (x == 0) || active1;
+    const TileSeen seen = tile_seen(x == 0 || active1, tq, tb, nb, local_b);
     const int row = tid & 127;                            // tile row == TMEM lane
     const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
     const int bi = (int)(i_tok >> 6);
     const int lo_band = bi + 1 - local_b;                 // first band block this row sees
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
-    if (tile_active) {
-      // Q row -> TMEM: a 32-bit word of the row already holds dims (2c, 2c+1) as the A operand wants
-      const uint4* qrow = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb +
-                                                         (int64_t)h * p.q_sh + i_tok * p.q_sn);
-      const bool in_range = i_tok < p.N;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t qv[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 u4 = in_range ? __ldg(qrow + half * 8 + c) : make_uint4(0, 0, 0, 0);
-          qv[4 * c] = u4.x; qv[4 * c + 1] = u4.y; qv[4 * c + 2] = u4.z; qv[4 * c + 3] = u4.w;
-        }
-        tmem_st32(lane_base + col_q(x) + half * 32, qv);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&ctl->q_ready[x]);
-    }
-
     float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
     float l = 0.f;
     bool ok = true;
-    int i = 0;                 // KV blocks this tile has taken part in
     PROF_DECL
     const bool prof_me = (tid & 127) == 0;
     (void)prof_me;
 
-    for (int u = 0; tile_active && u < nkv; ++u) {
-      const int jb = tb.block(u);
-      if (!tile_sees(tile_active, tq, jb, nb, sink_b, local_b)) continue;
+    for (int i = 0; i < seen.total; ++i) {
+      const int jb = tb.block(seen.entry(i));
       ok = mbar_wait(&ctl->s_full[x], i & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       PROF_ADD(0, prof_me);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + col_s(x);
       uint32_t sv[64];
       {
         uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
         uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
-        tmem_ld32(s_addr, lo32);
-        tmem_ld32(s_addr + 32, hi32);
+        if (!(MOA_PREFILL_DBG & 2)) {
+        tmem_ld32(lane_base + col_s(x), lo32);
+        tmem_ld32(lane_base + col_s(x) + 32, hi32);
         tmem_wait_ld();
+        } else { for (int c = 0; c < 64; ++c) sv[c] = __float_as_uint(0.01f * (float)(c + row)); }
       }
+      // S is in registers: let the tensor core start this tile's next S
+      tc_fence_before();
+      mbar_arrive(&ctl->s_free[x]);
       PROF_ADD(1, prof_me);
       const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
       if (edge) {
@@ -543,9 +592,17 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 #endif
       l = fmaf(l, factor, (ls[0] + ls[1]) + (ls[2] + ls[3]));
       PROF_ADD(2, prof_me);
-      // P row -> TMEM, over the S columns just read (two values per column, even key in the low half)
-      tmem_st32(s_addr, pk);
-      // S of this block is complete, so the tile's previous P.V (queued before it) is too: O may be touched
+      // the tile's previous P.V must be finished before P is overwritten or O rescaled
+      if (i > 0) {
+        ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      PROF_ADD(3, prof_me);
+      // P row -> TMEM (two values per column, even key in the low half)
+      if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_p(x), pk);
+      else if (pk[3] == 0x12345678u) l += 1.f;
       if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < kD; c0 += 32) {
@@ -560,16 +617,15 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&ctl->p_full[x]);
-      PROF_ADD(3, prof_me);
-      ++i;
+      PROF_ADD(4, prof_me);
     }
 
-    PROF_FLUSH(0, prof_me);
-    if (ok && i > 0) {
+    PROF_FLUSH(0, prof_me && x == 0);
+    if (ok && seen.total > 0) {
       ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && i > 0) {
+    if (ok && seen.total > 0) {
       tc_fence_after();
       const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
       const bool store = i_tok < p.N;
@@ -654,15 +710,15 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_
 }
 
 template <typename T, bool F32>
-int launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, dim3 grid,
-                   cudaStream_t stream) {
+int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
+                   dim3 grid, cudaStream_t stream) {
   auto kern = moa_prefill_kernel<T, F32>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     MOA_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured = true;
   }
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(mk, mv, p);
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   MOA_CUDA_CHECK(cudaGetLastError());
   return MOA_OK;
 }
@@ -694,12 +750,12 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
                   ((uintptr_t)out % 16 == 0),
               "prefill: pointers must be 16-byte aligned");
   MOA_REQUIRE(o_sb % 8 == 0 && o_sn % 8 == 0 && o_sh % 8 == 0, "prefill: out strides must be multiples of 8 elements");
-  CUtensorMap mk, mv;
+  CUtensorMap mq, mk, mv;
   int rc;
+  if ((rc = make_map(&mq, q, dtype, B, H, N, q_sb, q_sh, q_sn, kBM)) != MOA_OK) return rc;
   if ((rc = make_map(&mk, k, dtype, B, H, N, k_sb, k_sh, k_sn, kBN)) != MOA_OK) return rc;
   if ((rc = make_map(&mv, v, dtype, B, H, N, v_sb, v_sh, v_sn, kBN)) != MOA_OK) return rc;
   PrefillParams p;
-  p.q = q; p.q_sb = q_sb; p.q_sh = q_sh; p.q_sn = q_sn;
   p.out = out; p.o_sb = o_sb; p.o_sn = o_sn; p.o_sh = o_sh;
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
@@ -707,9 +763,9 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   dim3 grid((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == MOA_F16) {
-    return out_f32 ? launch_prefill<__half, true>(mk, mv, p, grid, st)
-                   : launch_prefill<__half, false>(mk, mv, p, grid, st);
+    return out_f32 ? launch_prefill<__half, true>(mq, mk, mv, p, grid, st)
+                   : launch_prefill<__half, false>(mq, mk, mv, p, grid, st);
   }
-  return out_f32 ? launch_prefill<__nv_bfloat16, true>(mk, mv, p, grid, st)
-                 : launch_prefill<__nv_bfloat16, false>(mk, mv, p, grid, st);
+  return out_f32 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, grid, st)
+                 : launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, grid, st);
 }
