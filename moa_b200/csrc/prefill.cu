@@ -29,6 +29,11 @@
 //
 // Every wait on an mbarrier is bounded: when it runs out the block sets an abort flag, records a
 // code in the status words, drains, frees its TMEM and returns.
+// Development probes (never compiled into the library): MOA_PREFILL_DBG bit 1 skips the softmax
+// threads' TMEM traffic, bit 2 skips the MMAs themselves (barrier handshakes only).
+#ifndef MOA_PREFILL_DBG
+#define MOA_PREFILL_DBG 0
+#endif
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -59,6 +64,8 @@ constexpr int kSmemV = kSmemK + kStages * kKBytes;
 constexpr int kSmemCtl = kSmemV + kStages * kKBytes;
 constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
 
+// the running max is only moved when a block exceeds it by more than this (log2 units)
+constexpr float kLazyMaxSlack = 8.f;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock: far above any legitimate wait
 constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drain loops of the abort path
 
@@ -82,11 +89,6 @@ struct Ctl {
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
 
-// Development probes (never compiled into the library): MOA_PREFILL_DBG bit 1 skips the softmax
-// threads' TMEM traffic, bit 2 skips the MMAs themselves (barrier handshakes only).
-#ifndef MOA_PREFILL_DBG
-#define MOA_PREFILL_DBG 0
-#endif
 #ifdef MOA_PREFILL_PROFILE
 #define PROF_DECL long long _pt = clock64(); long long _pa[16] = {0}; const int _pbase = 0;
 #define PROF_ADD(slot, cond)                     \
@@ -115,6 +117,7 @@ struct PrefillParams {
   int B, H;
   int64_t N;
   float scale_log2;
+  int heads_fastest;
   int32_t* status;
 };
 
@@ -303,8 +306,12 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nsuper = (int)((p.N + 2 * kBM - 1) / (2 * kBM));
-  const int st = nsuper - 1 - (int)blockIdx.x;  // heaviest super-tiles are scheduled first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Blocks are dispatched with x fastest, heaviest super-tiles first.  Long sequences put the tiles
+  // of one head next to each other (neighbours share their K/V band in L2); short ones put the heads
+  // next to each other so that every head's heavy tiles start early.
+  const int b = blockIdx.z;
+  const int h = p.heads_fastest ? blockIdx.x : blockIdx.y;
+  const int st = nsuper - 1 - (int)(p.heads_fastest ? blockIdx.y : blockIdx.x);
   const int nb = (int)((p.N + kBN - 1) / kBN);
   const int sink_b = p.sink_blocks[h], local_b = p.local_blocks[h];
   const int t0 = 2 * st, t1 = 2 * st + 1;
@@ -570,7 +577,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       // lazy rescale: move the reference max only when it grew by more than 2^8
       float factor = 1.f;
-      if (mt > m_used + 8.f) {
+      if (mt > m_used + kLazyMaxSlack) {
         factor = (m_used == -INFINITY) ? 1.f : exp2f(m_used - mt);
         m_used = mt;
       }
@@ -733,7 +740,8 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
                                int dtype, int out_f32, int32_t* status, moa_stream_t stream) {
   using namespace moa;
   MOA_REQUIRE(q && k && v && out && sink_blocks && local_blocks && status, "prefill: null pointer");
-  MOA_REQUIRE(B > 0 && H > 0 && N > 0 && B <= 65535 && H <= 65535, "prefill: bad shape");
+  MOA_REQUIRE(B > 0 && H > 0 && N > 0 && B <= 65535, "prefill: bad shape");
+  MOA_REQUIRE((N + 255) / 256 < 148 || H <= 65535, "prefill: too many heads for one launch");
   MOA_REQUIRE(N < (1LL << 31) - 512, "prefill: sequence too long");
   MOA_REQUIRE(sm_scale > 0.f, "prefill: sm_scale must be positive");
   if (D != kD) {
@@ -760,7 +768,10 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   const int nsuper = (int)((N + 2 * kBM - 1) / (2 * kBM));
-  dim3 grid((unsigned)nsuper, (unsigned)H, (unsigned)B);
+  // fewer super-tiles per head than SMs: interleave the heads
+  p.heads_fastest = (nsuper < 148 && H <= 65535) ? 1 : 0;
+  dim3 grid = p.heads_fastest ? dim3((unsigned)H, (unsigned)nsuper, (unsigned)B)
+                              : dim3((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == MOA_F16) {
     return out_f32 ? launch_prefill<__half, true>(mq, mk, mv, p, grid, st)
