@@ -45,9 +45,12 @@ WINDOWS = (256, 512, 1024, 2048, 4096)
 SINK = 64
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
-# DRAM bytes per decode launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# capture profiles/decode_cfg1_ncu.md; None until a capture has been made for the current kernel.
-DECODE_DRAM_BYTES_PER_LAUNCH = None
+# DRAM bytes per byte of algorithmic traffic for the decode kernel (dram__bytes_read.sum +
+# dram__bytes_write.sum over moa_b200.decode_bytes) from the ncu capture summarised in
+# profiles/decode_config1_ncu.md (taken at batch 4; traffic grows in proportion to the rows streamed).
+DECODE_DRAM_TRAFFIC_RATIO = 1.027
+# DRAM bytes per prefill launch relative to "Q, K, V read once, O written once" (profiles/prefill_config3_ncu.md)
+PREFILL_DRAM_TRAFFIC_RATIO = 0.967
 
 
 def config1_caps(seed: int):
@@ -243,7 +246,8 @@ def prefill_leg(device, peaks_tf, which, N=65536):
         return {"workload": f"config3 one layer: block-sparse prefill B1 H32 N{N} D128 bf16",
                 "tflops_band_dense_equiv": tf, "ms_per_layer": ms / iters, "flop_per_layer": flops,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks_tf, "unit": "TFLOP/s",
-                             "frac": tf / peaks_tf, "peak_source": which, "traffic": None}}
+                             "frac": tf / peaks_tf, "peak_source": which,
+                             "traffic": PREFILL_DRAM_TRAFFIC_RATIO * 4 * Hp * N * D * 2}}
     except Exception as exc:  # the decode headline must still be reported
         return {"error": f"{type(exc).__name__}: {exc}"}
 
@@ -330,7 +334,8 @@ def run_gpu(args):
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_source": which,
-                         "algorithmic_bytes_per_launch": bytes_per_launch, "traffic": DECODE_DRAM_BYTES_PER_LAUNCH},
+                         "algorithmic_bytes_per_launch": bytes_per_launch,
+                         "traffic": DECODE_DRAM_TRAFFIC_RATIO * bytes_per_launch},
             "clocks": clocks,
         }
         if prefill is not None:
