@@ -1,0 +1,75 @@
+"""Head sharding across the GPUs of one node.
+
+Heads are independent in attention and each owns its ring cache, so the path shards by heads with no
+exchange inside attention.  Where a whole layer runs, the per-rank outputs ``(B, q, H/G, D)`` are
+all-gathered into ``(B, q, H, D)`` before ``o_proj`` (NCCL over NVLink; ``gloo`` on CPU in the tests).
+One process per GPU (``torchrun``); nothing here touches peer memory directly.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .plan import shard_heads
+
+
+def init_process_group(backend: Optional[str] = None) -> None:
+    """``torchrun``-style initialisation (RANK / WORLD_SIZE / MASTER_* from the environment)."""
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    if backend == "nccl":
+        local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        dist.init_process_group(backend)
+
+
+class HeadSharding:
+    """Which heads of one layer live on which rank, balanced by per-head cost (cache capacity for
+    decode bytes, visited blocks for prefill flops) with longest-processing-time packing.
+
+    ``order`` is the head order after sharding (rank 0's heads, then rank 1's, ...): permuting the
+    q/k/v row blocks and o_proj column blocks by it (``permute_attention_projection`` /
+    ``permute_output_projection``) makes every rank's shard a contiguous slice, the same mechanism the
+    reference uses for ``permute_head``."""
+
+    def __init__(self, costs: Sequence[float], world_size: int, rank: int, group=None):
+        self.world_size, self.rank, self.group = world_size, rank, group
+        self.shards: List[List[int]] = shard_heads(costs, world_size)
+        self.order: List[int] = [h for s in self.shards for h in s]
+        self.local_heads: List[int] = self.shards[rank]
+        self.heads_per_rank = len(self.local_heads)
+        self._gather_buffers: Dict = {}
+
+    def slice_plan(self, values: Sequence) -> List:
+        """Per-head values (capacities, alphas, ...) of this rank's heads, in shard order."""
+        return [values[h] for h in self.local_heads]
+
+    def all_gather(self, local: Tensor) -> Tensor:
+        """``(B, q, H/G, D)`` of every rank -> ``(B, q, H, D)`` in ``order``.  The collective writes
+        into a cached ``(G*B, q, H/G, D)`` buffer; one small permuting copy puts the ranks' heads
+        next to each other."""
+        if self.world_size == 1:
+            return local
+        B, q, Hl, D = local.shape
+        key = (local.device, local.dtype, B, q, Hl, D)
+        buf = self._gather_buffers.get(key)
+        if buf is None:
+            buf = torch.empty(self.world_size * B, q, Hl, D, dtype=local.dtype, device=local.device)
+            self._gather_buffers[key] = buf
+        dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)   # rank r fills rows [r*B, (r+1)*B)
+        return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
+
+    def unpermute(self, gathered: Tensor) -> Tensor:
+        """``(B, q, H, D)`` in shard order -> original head order (for checks against an unsharded run)."""
+        inv = torch.empty(len(self.order), dtype=torch.long, device=gathered.device)
+        inv[torch.tensor(self.order, device=gathered.device)] = torch.arange(len(self.order), device=gathered.device)
+        return gathered[:, :, inv]

@@ -321,3 +321,62 @@ def decode_bytes(batch: int, valid_lengths: Sequence[int], d: int, itemsize: int
     """K and V rows read for every valid slot, plus q read, o write and the new K/V rows."""
     h = len(valid_lengths)
     return batch * int(sum(valid_lengths)) * d * 2 * itemsize + 4 * batch * h * d * itemsize
+
+
+# --------------------------------------------------------------------------------------
+# one attention layer      MoA/models/llama/modeling_llama.py:206-332 (LlamaMixtureAttention.forward)
+# --------------------------------------------------------------------------------------
+def rope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables of shape (B, q, D) in fp32, as the Llama rotary embedding builds them:
+    inv_freq = theta^(-2i/D), angles duplicated over the two halves of the head dim."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    freqs = position_ids[:, :, None].float() * inv_freq[None, None, :]
+    emb = torch.cat([freqs, freqs], dim=-1)
+    return emb.cos(), emb.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x (B, H, q, D): x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x[D/2:], x[:D/2])."""
+    d = x.shape[-1]
+    rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], dim=-1)
+    return x * cos[:, None] + rot * sin[:, None]
+
+
+def attention_layer_fp32(
+    hidden: torch.Tensor,
+    wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, wo: torch.Tensor,
+    num_heads: int,
+    position_ids: torch.Tensor,
+    cache: "RingCacheOracle",
+    layer: int,
+    rope_theta: float = 10000.0,
+    cache_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """fp32 restatement of one MoA attention layer: q/k/v projection -> view (B,H,q,D) -> RoPE ->
+    cache.update -> sparse prefill (q_len > 1) or decode over the ring (q_len == 1) -> o_proj.
+    Q/K/V are rounded to ``cache_dtype`` where the reference holds them in the model dtype, so the
+    cache payload can be compared bit-for-bit.  Returns (B, q, hidden) fp32."""
+    B, q_len, hid = hidden.shape
+    D = wq.shape[0] // num_heads
+    x = hidden.float()
+    q = (x @ wq.float().T).view(B, q_len, num_heads, D).transpose(1, 2)
+    k = (x @ wk.float().T).view(B, q_len, num_heads, D).transpose(1, 2)
+    v = (x @ wv.float().T).view(B, q_len, num_heads, D).transpose(1, 2)
+    cos, sin = rope_cos_sin(position_ids, D, rope_theta)
+    q = apply_rope(q, cos, sin).to(cache_dtype)
+    k = apply_rope(k, cos, sin).to(cache_dtype)
+    v = v.to(cache_dtype)
+    sm = D ** -0.5
+    np_dtype = np.float16 if cache_dtype == torch.float16 else np.float32
+    to_np = (lambda t: t.contiguous().numpy()) if cache_dtype == torch.float16 else (lambda t: t.float().contiguous().numpy())
+    if q_len > 1:
+        cache.update(to_np(k), to_np(v), layer)
+        sink_b = (cache.static_cache_size[layer] // BLOCK).tolist()
+        local_b = (cache.circular_cache_size[layer] // BLOCK).tolist()
+        attn = prefill_attention_fp32(q, k, v, sm, sink_b, local_b)            # (B, q, H, D)
+    else:
+        kc, vc = cache.update(to_np(k), to_np(v), layer)
+        attn = decode_attention_fp32(q, torch.from_numpy(kc.astype(np.float32)), torch.from_numpy(vc.astype(np.float32)),
+                                     torch.from_numpy(cache.cache_head_start_index[layer]),
+                                     torch.from_numpy(cache.cache_valid_length[layer]), sm)
+    return attn.reshape(B, q_len, num_heads * D) @ wo.float().T

