@@ -67,7 +67,7 @@ const char* moa_last_error_detail(void);
  *                moa_decode_workspace_init(); reusable by later calls on the same stream.
  *                Two launches that overlap in time must not share a workspace.
  *   chunk        rows of the flattened cache per thread block; 0 lets the library choose
- *                (128..1024 by problem size).  moa_decode_workspace_bytes must be asked with
+ *                (128..2048 by problem size).  moa_decode_workspace_bytes must be asked with
  *                the same chunk value that is passed here.
  * ------------------------------------------------------------------------------------------ */
 int64_t moa_decode_workspace_bytes(int B, int H, int D, int64_t S, int chunk);

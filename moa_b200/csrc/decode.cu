@@ -21,17 +21,22 @@ namespace {
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kTileIters = 8;  // 16-byte loads of K (and of V) in flight per thread
-constexpr int kMinChunk = 128, kMaxChunk = 1024;
+constexpr int kMinChunk = 128, kMaxChunk = 2048;
 
 // Rows per block when the caller passes chunk = 0.  A block pays a fixed latency chain (metadata,
-// partial write, ticket) whatever it streams, so chunks should be as long as the problem allows
-// while still giving every SM about two rounds of four resident blocks (148 SMs): the smallest
-// power of two >= B*S / (148*4*2), kept within [128, 1024].  Config 1 (B16, S=67k) gets 1024.
+// partial write, ticket) whatever it streams, so chunks should be long; and the grid should fill the
+// 148 SMs x 4 resident blocks in whole rounds.  Take the smallest number of rounds whose chunk
+// (rows of one batch row / blocks per batch row, rounded up to 32) stays within kMaxChunk.
+// Config 1 (B16, S = 67k): one round of 592 blocks, 1824 rows each.
 inline int auto_chunk(int B, int64_t S) {
-  const int64_t want = (int64_t)B * S / (148 * 4 * 2);
-  int chunk = kMinChunk;
-  while (chunk < want && chunk < kMaxChunk) chunk *= 2;
-  return chunk;
+  const int64_t slots = 148 * 4;
+  for (int rounds = 1; rounds <= 16; ++rounds) {
+    const int64_t per_row = (rounds * slots) / B > 0 ? (rounds * slots) / B : 1;
+    int64_t chunk = (S + per_row - 1) / per_row;
+    chunk = (chunk + 31) / 32 * 32;
+    if (chunk <= kMaxChunk) return (int)(chunk < kMinChunk ? kMinChunk : chunk);
+  }
+  return kMaxChunk;
 }
 
 struct DecodeParams {
