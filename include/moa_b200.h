@@ -80,6 +80,23 @@ int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_ne
                    void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * moa_decode_rope_fwd: the fused-append decode step with the rotary embedding folded in.
+ * Stands for the decode-time sequence of LlamaMixtureAttention.forward
+ * (MoA/models/llama/modeling_llama.py:252-326): apply_rotary_pos_emb(q, k) -> cache.update ->
+ * attention, in one launch.  q and k_new are the raw projection outputs; rope_cos / rope_sin are
+ * this step's (B, D) tables in the tensors' dtype (the position_embeddings the model computes once
+ * per forward, Llama rotate_half convention).  The rotated K row is what is stored in the cache.
+ * Everything else as moa_decode_fwd with k_new/v_new given.
+ * ------------------------------------------------------------------------------------------ */
+int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                        const void* rope_cos, const void* rope_sin,
+                        void* out, int64_t out_batch_stride, int64_t out_head_stride,
+                        const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                        int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                        int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                        void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * moa_decode_fwd_static: moa_decode_fwd without the workspace argument.  It has no counterpart
  * in the reference; it exists for hosts that cannot allocate device memory on the decode path
  * (a server whose KV-cache pool already owns all free HBM, a plugin that must not trigger

@@ -19,7 +19,7 @@ SYMBOLS = (
     "moa_abi_version", "moa_strerror", "moa_last_error_detail",
     "moa_decode_workspace_bytes", "moa_decode_workspace_init", "moa_decode_fwd",
     "moa_cache_append", "moa_cache_scan_mask", "moa_cache_fill", "moa_prefill_fwd",
-    "moa_decode_fwd_static",
+    "moa_decode_fwd_static", "moa_decode_rope_fwd",
 )
 
 
@@ -46,6 +46,8 @@ def _load() -> ctypes.CDLL:
     lib.moa_decode_workspace_bytes.argtypes = [I, I, I, I64, I]
     lib.moa_decode_workspace_init.argtypes = [P, I64, P]
     lib.moa_decode_fwd.argtypes = [P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, P, I64, I, P]
+    lib.moa_decode_rope_fwd.argtypes = [P, P, P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, P, I64, I, P]
+    lib.moa_decode_rope_fwd.restype = c_int
     lib.moa_decode_fwd_static.argtypes = [P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, I, P]
     lib.moa_decode_fwd_static.restype = c_int
     lib.moa_cache_append.argtypes = [P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, I, P]

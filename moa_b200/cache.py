@@ -241,12 +241,16 @@ class StaticCircularCache:
 
     # ------------------------------------------------------------------ fused decode step
     def decode_attention(self, query_states: Tensor, key_states: Tensor, value_states: Tensor, layer_idx: int,
-                         sm_scale: float, out: Optional[Tensor] = None) -> Tensor:
+                         sm_scale: float, out: Optional[Tensor] = None,
+                         rope: Optional[Tuple[Tensor, Tensor]] = None) -> Tensor:
         """One decode step of one layer in one launch: append the new ``(B, H, 1, D)`` K/V rows at
         the ring's write index, attend over the cache including the new token, advance the
         bookkeeping.  Same result as ``update(...)`` followed by
         ``mixture_of_sparse_attention(...)``.  Returns ``(B, 1, H, D)``; ``out`` may be a
-        pre-allocated tensor (or a ``(B, 1, H', D)`` slice of a wider gather buffer)."""
+        pre-allocated tensor (or a ``(B, 1, H', D)`` slice of a wider gather buffer).
+        ``rope=(cos, sin)``, tables of shape ``(B, 1, D)`` or ``(B, D)`` in the cache dtype, makes the
+        kernel apply the rotary embedding (Llama ``rotate_half`` convention) to ``query_states`` and
+        ``key_states`` itself; they are then the raw projection outputs."""
         H = self.num_head_for_each_layer[layer_idx]
         B, D, S = self.batch_size, self.head_dim, self.layer_cache_size[layer_idx]
         device = query_states.device
@@ -265,6 +269,21 @@ class StaticCircularCache:
         ws = self.decode_workspace(layer_idx, device)
         if layer_idx == 0:
             self.cache_position += 1
+        if rope is not None:
+            cos, sin = rope
+            cos, sin = cos.reshape(B, D).contiguous(), sin.reshape(B, D).contiguous()
+            assert cos.dtype == self.dtype and sin.dtype == self.dtype and cos.device == device
+            with torch.cuda.device(device):
+                _lib.check("moa_decode_rope_fwd", lib.moa_decode_rope_fwd(
+                    q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),
+                    k_new.data_ptr(), v_new.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), out.stride(0),
+                    out.stride(2), self.cache_head_start_index[layer_idx].data_ptr(),
+                    self.cache_valid_length[layer_idx].data_ptr(), self.cache_update_index[layer_idx].data_ptr(),
+                    self.mask_cache[layer_idx].data_ptr(), self.static_cache_size[layer_idx].data_ptr(),
+                    self._kv_len[layer_idx], B, H, D, S, float(sm_scale), _lib.dtype_code(self.dtype), ws.data_ptr(),
+                    ws.numel(), self.decode_chunk, _lib.current_stream(device)))
+            self._kv_len[layer_idx] += 1
+            return out
         with torch.cuda.device(device):
             _lib.check("moa_decode_fwd", lib.moa_decode_fwd(
                 q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),

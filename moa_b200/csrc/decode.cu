@@ -24,12 +24,11 @@ constexpr int kTileIters = 8;  // 16-byte loads of K (and of V) in flight per th
 constexpr int kMinChunk = 128, kMaxChunk = 2048;
 
 // Rows per block when the caller passes chunk = 0.  A block pays a fixed latency chain (metadata,
-// partial write, ticket) whatever it streams, so chunks should be long; and the grid should fill the
-// 148 SMs x 4 resident blocks in whole rounds.  Take the smallest number of rounds whose chunk
-// (rows of one batch row / blocks per batch row, rounded up to 32) stays within kMaxChunk.
-// Config 1 (B16, S = 67k): one round of 592 blocks, 1824 rows each.
-inline int auto_chunk(int B, int64_t S) {
-  const int64_t slots = 148 * 4;
+// partial write, ticket) whatever it streams, so chunks should be long; and the grid should fill
+// every resident-block slot of the GPU (`slots` = SMs x blocks per SM, asked from the runtime) in
+// whole rounds.  Take the smallest number of rounds whose chunk (rows of one batch row / blocks per
+// batch row, rounded up to 32) stays within kMaxChunk.
+inline int auto_chunk_for(int B, int64_t S, int64_t slots) {
   for (int rounds = 1; rounds <= 16; ++rounds) {
     const int64_t per_row = (rounds * slots) / B > 0 ? (rounds * slots) / B : 1;
     int64_t chunk = (S + per_row - 1) / per_row;
@@ -38,6 +37,8 @@ inline int auto_chunk(int B, int64_t S) {
   }
   return kMaxChunk;
 }
+int decode_slots();  // defined after the kernel
+inline int auto_chunk(int B, int64_t S) { return auto_chunk_for(B, S, decode_slots()); }
 
 struct DecodeParams {
   const void* q;
@@ -52,6 +53,8 @@ struct DecodeParams {
   int64_t* update_index;
   int64_t* mask_cache;
   const int64_t* static_size;
+  const void* rope_cos;  // (B, D) or nullptr: rotary embedding of this step applied to q and k_new in the kernel
+  const void* rope_sin;
   int64_t kv_len;
   int B, H;
   int64_t S;
@@ -73,6 +76,29 @@ __device__ __forceinline__ int find_head(const int64_t* hs, int H, int64_t row, 
     count += __popc(__ballot_sync(0xffffffffu, le));
   }
   return count > 0 ? count - 1 : 0;
+}
+
+// Rotary embedding of the 8 dims [8*l16, 8*l16+8) of one row held by this lane:
+//   x' = x*cos + rotate_half(x)*sin,  rotate_half(x)[d] = d < D/2 ? -x[d + D/2] : x[d - D/2]
+// (the Llama convention).  The partner dims live in lane l16 ^ (LPR/2) of the LPR lanes that share
+// the row.  Computed in fp32, rounded once to T.  `mask` names the lanes that execute the call.
+template <typename T, int LPR>
+__device__ __forceinline__ uint4 rope8(const uint4& x, const T* cos_row, const T* sin_row, int l16, unsigned long long mask) {
+  float xf[8], cf[8], sf[8];
+  unpack8<T>(x, xf);
+  unpack8<T>(*reinterpret_cast<const uint4*>(cos_row + l16 * 8), cf);
+  unpack8<T>(*reinterpret_cast<const uint4*>(sin_row + l16 * 8), sf);
+  const bool upper = l16 >= LPR / 2;
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float partner = __shfl_xor_sync((unsigned)mask, xf[j], LPR / 2);
+    r[j] = fmaf(xf[j], cf[j], (upper ? partner : -partner) * sf[j]);
+  }
+  uint4 o;
+  o.x = Cvt<T>::pack(r[0], r[1]); o.y = Cvt<T>::pack(r[2], r[3]);
+  o.z = Cvt<T>::pack(r[4], r[5]); o.w = Cvt<T>::pack(r[6], r[7]);
+  return o;
 }
 
 template <typename T, int D>
@@ -116,21 +142,32 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
     const T* knew = fused ? reinterpret_cast<const T*>(p.k_new) + bh * D : nullptr;
     const T* vnew = fused ? reinterpret_cast<const T*>(p.v_new) + bh * D : nullptr;
 
-    // Fused append: the block whose chunk holds the write slot stores the new K and V rows.
-    // No other block reads that row (it lies in this chunk only), and this block takes the row's
-    // values from k_new/v_new below, so the store does not race with any load.
-    if (fused && upd >= lo && upd < hi && upd >= hs && upd < he && warp == 0 && lane < 2 * LPR) {
-      const bool is_v = lane >= LPR;
-      const int l16 = lane % LPR;
-      const T* src = (is_v ? vnew : knew) + l16 * 8;
-      T* dst = const_cast<T*>(is_v ? vc : kc) + upd * D + l16 * 8;
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    // Fused append: the block whose chunk holds the write slot stores the new K and V rows (K with the
+    // rotary embedding applied when cos/sin are given), then the whole block reads them back from the
+    // cache like any other row.  No other block reads that row: it lies in this chunk only.
+    const bool rope = p.rope_cos != nullptr;
+    const T* cos_row = rope ? reinterpret_cast<const T*>(p.rope_cos) + (int64_t)b * D : nullptr;
+    const T* sin_row = rope ? reinterpret_cast<const T*>(p.rope_sin) + (int64_t)b * D : nullptr;
+    if (fused && upd >= lo && upd < hi && upd >= hs && upd < he) {   // uniform over the block
+      if (warp == 0) {
+        const int l16 = lane % LPR;
+        if (lane < LPR) {
+          uint4 ku = *reinterpret_cast<const uint4*>(knew + l16 * 8);
+          if (rope) ku = rope8<T, LPR>(ku, cos_row, sin_row, l16, (1ull << LPR) - 1ull);
+          *reinterpret_cast<uint4*>(const_cast<T*>(kc) + upd * D + l16 * 8) = ku;
+        } else if (lane < 2 * LPR) {
+          *reinterpret_cast<uint4*>(const_cast<T*>(vc) + upd * D + l16 * 8) =
+              *reinterpret_cast<const uint4*>(vnew + l16 * 8);
+        }
+      }
+      __syncthreads();
     }
 
-    // q slice of this lane, pre-scaled so that softmax runs in base 2
+    // q slice of this lane (rotated if asked), pre-scaled so that softmax runs in base 2
     float qf[8];
     {
-      const uint4 qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + bh * D + li * 8);
+      uint4 qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + bh * D + li * 8);
+      if (rope) qu = rope8<T, LPR>(qu, cos_row, sin_row, li, 0xffffffffull);
       unpack8<T>(qu, qf);
 #pragma unroll
       for (int j = 0; j < 8; ++j) qf[j] *= p.scale_log2;
@@ -147,12 +184,12 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
       for (int i = 0; i < kTileIters; ++i) {
         // rows past the segment re-read its last row (a valid address); their score is masked
         const int64_t r = min(row0 + i * RPI + sub, seg_hi - 1);
-        kr[i] = ld_stream16((r == upd) ? knew + li * 8 : kc + r * D + li * 8);
+        kr[i] = ld_stream16(kc + r * D + li * 8);
       }
 #pragma unroll
       for (int i = 0; i < kTileIters; ++i) {
         const int64_t r = min(row0 + i * RPI + sub, seg_hi - 1);
-        vr[i] = ld_stream16((r == upd) ? vnew + li * 8 : vc + r * D + li * 8);
+        vr[i] = ld_stream16(vc + r * D + li * 8);
       }
       float s[kTileIters];
       float mt = -INFINITY;
@@ -263,6 +300,25 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
   }
 }
 
+// Resident-block slots of the current device for this kernel; 148 x 5 if no device can be asked
+// (a build or test machine without a GPU).
+int decode_slots() {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  int dev = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moa_decode_kernel<__half, 128>, kDecodeThreads, 0) ==
+          cudaSuccess &&
+      sms > 0 && per_sm > 0) {
+    cached = sms * per_sm;
+  } else {
+    (void)cudaGetLastError();
+    return 148 * 5;
+  }
+  return cached;
+}
+
 template <typename T>
 int launch_decode(const DecodeParams& p, int D, dim3 grid, cudaStream_t stream) {
   switch (D) {
@@ -294,11 +350,13 @@ int decode_launch_with_scratch(const void* q, void* k_cache, void* v_cache, cons
                                int64_t* valid_len, int64_t* update_index, int64_t* mask_cache,
                                const int64_t* static_size, int64_t kv_len, int B, int H, int D, int64_t S,
                                float sm_scale, int dtype, void* workspace, int64_t workspace_bytes, int chunk,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const void* rope_cos = nullptr, const void* rope_sin = nullptr) {
   MOA_REQUIRE(q && k_cache && v_cache && out && head_start && valid_len, "decode: null pointer");
   MOA_REQUIRE((k_new == nullptr) == (v_new == nullptr), "decode: k_new and v_new must both be given or both be NULL");
   MOA_REQUIRE(B > 0 && H > 0 && S > 0 && B <= 65535, "decode: bad shape");
   if (k_new) MOA_REQUIRE(update_index && static_size, "decode: fused append needs update_index and static_size");
+  MOA_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "decode: rope_cos and rope_sin go together");
+  MOA_REQUIRE(rope_cos == nullptr || k_new != nullptr, "decode: the rotary embedding is applied in the fused-append mode only");
   if (chunk <= 0) chunk = auto_chunk(B, S);
   const WsLayout w = ws_layout(B, H, D, S, chunk);
   if (!workspace || workspace_bytes < w.total) {
@@ -310,6 +368,7 @@ int decode_launch_with_scratch(const void* q, void* k_cache, void* v_cache, cons
   p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_new = k_new; p.v_new = v_new; p.out = out;
   p.out_bs = out_bs; p.out_hs = out_hs; p.head_start = head_start; p.valid_len = valid_len;
   p.update_index = update_index; p.mask_cache = mask_cache; p.static_size = static_size; p.kv_len = kv_len;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin;
   p.B = B; p.H = H; p.S = S; p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.tickets = reinterpret_cast<int*>(workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.ticket_bytes);
@@ -349,6 +408,19 @@ int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_ne
 }
 
 }  // extern "C"
+
+extern "C" int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                                   const void* rope_cos, const void* rope_sin, void* out, int64_t out_batch_stride,
+                                   int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
+                                   int64_t* update_index, int64_t* mask_cache, const int64_t* static_size,
+                                   int64_t kv_len, int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                                   void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream) {
+  MOA_REQUIRE(rope_cos && rope_sin && k_new && v_new, "decode_rope: needs k_new, v_new, rope_cos and rope_sin");
+  return moa::decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
+                                         head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H,
+                                         D, S, sm_scale, dtype, workspace, workspace_bytes, chunk,
+                                         (cudaStream_t)stream, rope_cos, rope_sin);
+}
 
 // ------------------------------------------------------------------------------------------------
 // Decode entry point that brings its own scratch (no workspace argument, no allocation).

@@ -94,11 +94,12 @@ class MoAAttention(nn.Module):
             assert position_ids is not None, "position_ids or position_embeddings are required"
             position_embeddings = rotary_cos_sin(position_ids, D, self.rope_theta, hidden_states.dtype)
         cos, sin = position_embeddings
-        q, k = apply_rotary_pos_emb(q, k, cos, sin)
         sm_scale = D ** -0.5
         if q_len == 1:
-            attn = past_key_value.decode_attention(q, k, v, self.layer_idx, sm_scale)       # (B, 1, H, D)
+            # one launch: rotary embedding of q and k, ring append, flash-decoding, bookkeeping
+            attn = past_key_value.decode_attention(q, k, v, self.layer_idx, sm_scale, rope=(cos, sin))   # (B, 1, H, D)
         else:
+            q, k = apply_rotary_pos_emb(q, k, cos, sin)
             past_key_value.update(k, v, self.layer_idx)
             attn = mixture_of_sparse_attention(
                 q, k, v, sm_scale=sm_scale, attention_mask=None, attention_dropout=0.0,

@@ -189,3 +189,31 @@ def test_full_size_config1_properties():
     out2 = moa_b200.mixture_of_sparse_attention(q, k2, v2, 1.0, head_start_index=hs, head_valid_length=valid)
     want = v2[bidx, win[None].expand(B, H)]
     assert (out2[:, 0].float() - want.float()).abs().max() < 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Dh", [128, 64])
+def test_rotary_embedding_inside_the_kernel_matches_rotating_first(dtype, Dh):
+    """decode_attention(..., rope=(cos, sin)) on raw q/k equals rotating q and k (fp32, one rounding)
+    and then calling the plain fused step; the rotated K row is what lands in the cache."""
+    from moa_b200.module import rotary_cos_sin
+    gen = torch.Generator().manual_seed(17)
+    B, caps = 3, [128, 320, 192]
+    H = len(caps)
+    mk = lambda: moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", dtype)
+    a, b = mk(), mk()
+    kp = torch.randn(B, H, 250, Dh, generator=gen).to(dtype).cuda()
+    vp = torch.randn(B, H, 250, Dh, generator=gen).to(dtype).cuda()
+    a.update(kp, vp, 0)
+    b.update(kp, vp, 0)
+    for step in range(4):
+        q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen).to(dtype).cuda() for _ in range(3))
+        pos = torch.tensor([[250 + step], [7 + step], [100000 + step]], device="cuda")
+        cos, sin = rotary_cos_sin(pos, Dh, 10000.0, dtype)
+        out_a = a.decode_attention(q, k1, v1, 0, Dh ** -0.5, rope=(cos, sin))
+        q_rot = orc.apply_rope(q.float().cpu(), cos.float().cpu(), sin.float().cpu()).to(dtype).cuda()
+        k_rot = orc.apply_rope(k1.float().cpu(), cos.float().cpu(), sin.float().cpu()).to(dtype).cuda()
+        out_b = b.decode_attention(q_rot, k_rot, v1, 0, Dh ** -0.5)
+        assert torch.equal(out_a, out_b), step
+    assert torch.equal(a.key_cache[0], b.key_cache[0]) and torch.equal(a.value_cache[0], b.value_cache[0])
+    assert torch.equal(a.cache_update_index[0], b.cache_update_index[0])
