@@ -252,6 +252,50 @@ def prefill_leg(device, peaks_tf, which, N=65536):
         return {"error": f"{type(exc).__name__}: {exc}"}
 
 
+def model_leg(device, steps: int = 8, warmup: int = 3, batch: int = 32, context: int = 16384, layers: int = 32):
+    """Informational: BASELINE config 2 — Vicuna-7B-16k architecture (32 layers, hidden 4096, 32 heads x 128,
+    FFN 11008, RoPE, fp16) with random-init weights, decode with batch 32 at 16k context on one GPU.
+    The per-layer plan is drawn as in config 0 with N = 16384; the ring caches are filled layer by layer
+    from random K/V (a 16k-token model prefill at batch 32 is not part of this leg).  One step = one new
+    token for every sequence through all layers (GEMMs are library kernels, attention is the fused
+    decode launch of this package)."""
+    import moa_b200
+
+    rng = np.random.RandomState(2000)
+    hidden, heads, ffn = 4096, 32, 11008
+    plan = {"alphas": [[float(rng.choice([128, 256, 512, 1024])) for _ in range(heads)] for _ in range(layers)],
+            "betas": [[float(rng.uniform(0, 0.5)) for _ in range(heads)] for _ in range(layers)]}
+    model = moa_b200.MoALlamaModel(layers, hidden, heads, ffn, vocab_size=32000, rope_theta=10000.0,
+                                   dtype=torch.float16, device=device)
+    gen = torch.Generator(device=device).manual_seed(2000)
+    for prm in model.parameters():
+        if prm.dim() > 1:
+            prm.data.normal_(0, 0.02, generator=gen)
+    model.set_mixture_of_attention(plan, permute_head=True, moa_max_new_token=1024)
+    cache = model.new_cache(batch, context)
+    kv_bytes = 0
+    for layer in range(layers):
+        k = torch.randn(batch, heads, context, 128, generator=gen, device=device, dtype=torch.float16)
+        cache.update(k, k, layer)          # same tensor for K and V: only sizes and traffic matter here
+        kv_bytes += 2 * batch * cache.layer_cache_size[layer] * 128 * 2
+        del k
+    torch.cuda.synchronize(device)
+    ids = torch.randint(0, 32000, (batch, 1), device=device, generator=gen)
+
+    def step(i):
+        model(ids, past_key_values=cache)
+
+    for i in range(warmup):
+        step(i)
+    ms, _ = time_region(step, steps, device, None)
+    weights = sum(prm.numel() for prm in model.parameters() if prm.dim() > 1 and prm is not model.embed_tokens.weight) * 2
+    per_step = ms / steps
+    return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
+                        f"{layers} layers, 1 GPU", "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
+            "kv_bytes_per_step": kv_bytes, "weight_bytes_per_step": weights,
+            "hbm_gbs": (kv_bytes + weights) / (per_step * 1e-3) / 1e9}
+
+
 def run_gpu(args):
     import moa_b200
 
@@ -273,6 +317,9 @@ def run_gpu(args):
     if args.leg == "prefill":
         hbm_peak, tf_peak, which = measured_peaks()
         print(json.dumps({"prefill": prefill_leg(device, tf_peak, which, args.prefill_n)}), flush=True)
+        return
+    if args.leg == "model":
+        print(json.dumps({"model": model_leg(device, steps=max(1, min(args.steps, 16)))}), flush=True)
         return
     seed = 1000 + rank
     caps = config1_caps(1000)       # same capacities on every rank; data differs by rank
@@ -358,7 +405,8 @@ def main():
     ap.add_argument("--impl", default="moa_b200", choices=["moa_b200", "reference"])
     ap.add_argument("--batch", type=int, default=16, help="batch size (16 = config 1; smaller only for profiler captures)")
     ap.add_argument("--fill-tokens", type=int, default=PREFILL_TOKENS, help="tokens the caches are filled from")
-    ap.add_argument("--leg", default="all", choices=["all", "prefill"], help="'prefill' runs only the prefill leg")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "model"],
+                    help="'prefill': only the prefill leg; 'model': whole-model decode of config 2 (informational)")
     ap.add_argument("--prefill-n", type=int, default=65536, help="sequence length of the prefill leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the informational prefill leg")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")

@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmoa_b200.so")
+#: the library next to this file; MOA_B200_LIB points at another build of it (kernel development)
+LIB_PATH = os.environ.get("MOA_B200_LIB") or os.path.join(HERE, "libmoa_b200.so")
 
 F16, BF16 = 0, 1
 

@@ -20,7 +20,10 @@ namespace {
 
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kTileIters = 8;  // 16-byte loads of K (and of V) in flight per thread
+#ifndef MOA_DECODE_TILE_ITERS
+#define MOA_DECODE_TILE_ITERS 8
+#endif
+constexpr int kTileIters = MOA_DECODE_TILE_ITERS;  // 16-byte loads of K (and of V) in flight per thread
 constexpr int kMinChunk = 128, kMaxChunk = 2048;
 
 // Rows per block when the caller passes chunk = 0.  A block pays a fixed latency chain (metadata,
