@@ -296,6 +296,45 @@ def model_leg(device, steps: int = 8, warmup: int = 3, batch: int = 32, context:
             "hbm_gbs": (kv_bytes + weights) / (per_step * 1e-3) / 1e9}
 
 
+def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int = 5):
+    """Informational: the attention part of one decode step of one BASELINE config 4 layer (Llama-3-70B as
+    MHA: 64 heads x 128, bf16, batch 64, per-head window drawn from U[1k, 16k] rounded to 64, plus 64 sinks,
+    rings full).  The 64 heads are placed on the ranks by cost (longest-processing-time packing); every rank
+    runs the fused decode launch on its shard and the outputs are all-gathered over NCCL into (B, 1, 64, D).
+    Strong scaling: the layer is fixed, the work per GPU shrinks with the number of GPUs."""
+    import moa_b200
+
+    Bl, Hl, Dl = 64, 64, 128
+    rng = np.random.RandomState(4000)
+    caps = [SINK + int(-(-int(w) // 64) * 64) for w in rng.uniform(1024, 16384, Hl)]
+    sh = moa_b200.HeadSharding(caps, world, rank, group=None)
+    mine = sh.slice_plan(caps)
+    gen = torch.Generator(device=device).manual_seed(4000 + rank)
+    cache = moa_b200.StaticCircularCache([mine], Bl, Dl, [[SINK] * len(mine)], device, torch.bfloat16)
+    fill = max(mine)
+    k = torch.randn(Bl, len(mine), fill, Dl, generator=gen, device=device, dtype=torch.bfloat16)
+    cache.update(k, k, 0)            # same tensor for K and V: only sizes and traffic matter here
+    del k
+    trio = [torch.randn(Bl, len(mine), 1, Dl, generator=gen, device=device, dtype=torch.bfloat16) for _ in range(3)]
+    out = torch.empty(Bl, 1, len(mine), Dl, dtype=torch.bfloat16, device=device)
+    sm = Dl ** -0.5
+
+    def step(i):
+        cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
+        sh.all_gather(out)
+
+    for i in range(warmup):
+        step(i)
+    ms, _ = time_region(step, steps, device, dist)
+    kv_bytes_all = moa_b200.decode_bytes(Bl, caps, Dl, 2)
+    loads = [sum(caps[h] for h in s) for s in sh.shards]
+    return {"workload": "config4 one layer, attention + all-gather: B64 H64 D128 bf16, windows U[1k,16k] + 64 sinks, "
+                        f"heads sharded over {world} GPU(s)", "us_per_step": ms / steps * 1e3,
+            "tokens_per_s": Bl / (ms / steps * 1e-3), "aggregate_hbm_gbs": kv_bytes_all / (ms / steps * 1e-3) / 1e9,
+            "allgather_bytes_per_step": Bl * Hl * Dl * 2 if world > 1 else 0,
+            "shard_imbalance": max(loads) / (sum(loads) / len(loads))}
+
+
 def run_gpu(args):
     import moa_b200
 
@@ -356,6 +395,7 @@ def run_gpu(args):
 
     hbm_peak, tf_peak, which = measured_peaks()
     prefill = prefill_leg(device, tf_peak, which, args.prefill_n) if (world == 1 and not args.no_prefill) else None
+    layer = layer_leg(device, dist, world, rank) if (world > 1 or args.leg == "layer") else None
     if dist is not None:
         dist.barrier()
     clocks = sampler.stop([win1, win2]) if sampler else None
@@ -387,6 +427,8 @@ def run_gpu(args):
         }
         if prefill is not None:
             line["prefill"] = prefill
+        if layer is not None:
+            line["layer_allgather"] = layer
         if world == 1 and not args.no_cpu_baseline:
             val, per_step, cores = cpu_decode_tok_per_s(caps, 30, 1000)
             line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
@@ -405,8 +447,9 @@ def main():
     ap.add_argument("--impl", default="moa_b200", choices=["moa_b200", "reference"])
     ap.add_argument("--batch", type=int, default=16, help="batch size (16 = config 1; smaller only for profiler captures)")
     ap.add_argument("--fill-tokens", type=int, default=PREFILL_TOKENS, help="tokens the caches are filled from")
-    ap.add_argument("--leg", default="all", choices=["all", "prefill", "model"],
-                    help="'prefill': only the prefill leg; 'model': whole-model decode of config 2 (informational)")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "model", "layer"],
+                    help="'prefill': only the prefill leg; 'model': whole-model decode of config 2; "
+                         "'layer': also time the config-4 attention layer with its all-gather (always on with N > 1)")
     ap.add_argument("--prefill-n", type=int, default=65536, help="sequence length of the prefill leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the informational prefill leg")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
