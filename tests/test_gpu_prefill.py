@@ -73,6 +73,13 @@ CASES = [
     (1, 4, 2048, [1, 1, 1, 0], [1, 3, 8, 31]),
     (1, 2, 1, [1, 1], [1, 1]),
     (1, 2, 37, [1, 1], [1, 1]),
+    # wide sinks: the two tiles of a block take part in different sink blocks near the diagonal
+    (1, 3, 1500, [5, 20, 3], [1, 3, 2]),
+    (2, 2, 777, [12, 2], [2, 1]),
+    # window wider than the sequence: dense causal
+    (1, 2, 900, [1, 0], [64, 100]),
+    # many heads, short sequence
+    (1, 40, 200, [1] * 40, [1 + (i % 4) for i in range(40)]),
 ]
 
 
