@@ -176,6 +176,27 @@ int moa_prefill_fwd(const void* q, const void* k, const void* v, void* out,
                     int B, int H, int64_t N, int D, float sm_scale, int dtype, int out_f32,
                     int32_t* status, moa_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * moa_rope_qk: rotary embedding of q and k in place, one pass over both.  Replaces
+ * apply_rotary_pos_emb(query_states, key_states, cos, sin) at MoA/models/llama/modeling_llama.py:252
+ * for the prefill (the decode step applies it inside moa_decode_rope_fwd).
+ *   q, k      (B, H, N, D) sharing the element strides (sb, sh, sn), D contiguous
+ *   cos, sin  (B, N, D) tables in the tensors' dtype, element strides (cos_batch_stride, cos_token_stride);
+ *             a batch stride of 0 shares one table among the batch rows
+ * ------------------------------------------------------------------------------------------ */
+int moa_rope_qk(void* q, void* k, int64_t sb, int64_t sh, int64_t sn, const void* cos, const void* sin,
+                int64_t cos_batch_stride, int64_t cos_token_stride, int B, int H, int64_t N, int D, int dtype,
+                moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * moa_selftest_bounded_wait: failure-detection self-test (no counterpart in the reference, which has
+ * no device-side waits).  Launches one thread that waits, for at most limit_cycles SM cycles, on an
+ * mbarrier nobody arrives at, through the same bounded-wait routine the prefill kernel uses.  After
+ * the kernel status[0] holds the wait code (non-zero) and status[1..3] the block/thread that gave up;
+ * the kernel returns normally.  status: device int32[4], zero on entry.
+ * ------------------------------------------------------------------------------------------ */
+int moa_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, moa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,7 +20,7 @@ SYMBOLS = (
     "moa_abi_version", "moa_strerror", "moa_last_error_detail",
     "moa_decode_workspace_bytes", "moa_decode_workspace_init", "moa_decode_fwd",
     "moa_cache_append", "moa_cache_scan_mask", "moa_cache_fill", "moa_prefill_fwd",
-    "moa_decode_fwd_static", "moa_decode_rope_fwd",
+    "moa_decode_fwd_static", "moa_decode_rope_fwd", "moa_selftest_bounded_wait", "moa_rope_qk",
 )
 
 
@@ -49,6 +49,10 @@ def _load() -> ctypes.CDLL:
     lib.moa_decode_fwd.argtypes = [P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, P, I64, I, P]
     lib.moa_decode_rope_fwd.argtypes = [P, P, P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, P, I64, I, P]
     lib.moa_decode_rope_fwd.restype = c_int
+    lib.moa_rope_qk.argtypes = [P, P, I64, I64, I64, P, P, I64, I64, I, I, I64, I, I, P]
+    lib.moa_rope_qk.restype = c_int
+    lib.moa_selftest_bounded_wait.argtypes = [P, I64, P]
+    lib.moa_selftest_bounded_wait.restype = c_int
     lib.moa_decode_fwd_static.argtypes = [P, P, P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, c_float, I, I, P]
     lib.moa_decode_fwd_static.restype = c_int
     lib.moa_cache_append.argtypes = [P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, I, P]

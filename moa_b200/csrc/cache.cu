@@ -160,10 +160,94 @@ __global__ void cache_fill_finalize_kernel(const int32_t* count, const int64_t* 
   update_index[i] = fill_slot(f, kv_len, f.n);  // cache_utils.py:1110
 }
 
+// ---- rotary embedding of q and k in place (modeling_llama.py:252) -----------------------------
+// One thread rotates 8 dims of the lower half of a row together with their partners in the upper half:
+//   x'[d] = x[d] cos[d] - x[d + D/2] sin[d],   x'[d + D/2] = x[d + D/2] cos[d + D/2] + x[d] sin[d + D/2]
+// (Llama rotate_half convention), fp32 arithmetic, one rounding.  Rows are (b, h, n); q and k share
+// the (b, n) tables.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) rope_qk_kernel(T* q, T* k, int64_t sb, int64_t sh, int64_t sn, const T* cos_t,
+                                                      const T* sin_t, int64_t cs_b, int64_t cs_n, int H, int64_t N,
+                                                      int64_t total) {
+  constexpr int TPR = D / 16;  // threads per row
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t rowi = idx / TPR;
+  if (rowi >= total) return;
+  const int part = (int)(idx % TPR);
+  const int64_t n = rowi % N, bh = rowi / N;
+  const int h = (int)(bh % H);
+  const int64_t b = bh / H;
+  const T* cr = cos_t + b * cs_b + n * cs_n;
+  const T* sr = sin_t + b * cs_b + n * cs_n;
+  float c_lo[8], c_hi[8], s_lo[8], s_hi[8];
+  unpack8<T>(*reinterpret_cast<const uint4*>(cr + part * 8), c_lo);
+  unpack8<T>(*reinterpret_cast<const uint4*>(cr + D / 2 + part * 8), c_hi);
+  unpack8<T>(*reinterpret_cast<const uint4*>(sr + part * 8), s_lo);
+  unpack8<T>(*reinterpret_cast<const uint4*>(sr + D / 2 + part * 8), s_hi);
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    T* row = (which == 0 ? q : k) + b * sb + (int64_t)h * sh + n * sn;
+    float lo[8], hi[8], olo[8], ohi[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(row + part * 8), lo);
+    unpack8<T>(*reinterpret_cast<const uint4*>(row + D / 2 + part * 8), hi);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      olo[j] = fmaf(lo[j], c_lo[j], -hi[j] * s_lo[j]);
+      ohi[j] = fmaf(hi[j], c_hi[j], lo[j] * s_hi[j]);
+    }
+    uint4 a, c;
+    a.x = Cvt<T>::pack(olo[0], olo[1]); a.y = Cvt<T>::pack(olo[2], olo[3]);
+    a.z = Cvt<T>::pack(olo[4], olo[5]); a.w = Cvt<T>::pack(olo[6], olo[7]);
+    c.x = Cvt<T>::pack(ohi[0], ohi[1]); c.y = Cvt<T>::pack(ohi[2], ohi[3]);
+    c.z = Cvt<T>::pack(ohi[4], ohi[5]); c.w = Cvt<T>::pack(ohi[6], ohi[7]);
+    *reinterpret_cast<uint4*>(row + part * 8) = a;
+    *reinterpret_cast<uint4*>(row + D / 2 + part * 8) = c;
+  }
+}
+
+template <typename T>
+int launch_rope(void* q, void* k, int64_t sb, int64_t sh, int64_t sn, const void* cos_t, const void* sin_t,
+                int64_t cs_b, int64_t cs_n, int B, int H, int64_t N, int D, cudaStream_t st) {
+  const int64_t total = (int64_t)B * H * N;
+  if (D == 128) {
+    const int64_t threads = total * 8;
+    rope_qk_kernel<T, 128><<<(unsigned)ceil_div64(threads, 256), 256, 0, st>>>((T*)q, (T*)k, sb, sh, sn, (const T*)cos_t,
+                                                                             (const T*)sin_t, cs_b, cs_n, H, N, total);
+  } else if (D == 64) {
+    const int64_t threads = total * 4;
+    rope_qk_kernel<T, 64><<<(unsigned)ceil_div64(threads, 256), 256, 0, st>>>((T*)q, (T*)k, sb, sh, sn, (const T*)cos_t,
+                                                                            (const T*)sin_t, cs_b, cs_n, H, N, total);
+  } else {
+    set_error_text("rope_qk: head_dim must be 64 or 128");
+    return MOA_ERR_UNSUPPORTED;
+  }
+  MOA_CUDA_CHECK(cudaGetLastError());
+  return MOA_OK;
+}
+
 }  // namespace
 }  // namespace moa
 
 extern "C" {
+
+int moa_rope_qk(void* q, void* k, int64_t sb, int64_t sh, int64_t sn, const void* cos_t, const void* sin_t,
+                int64_t cos_batch_stride, int64_t cos_token_stride, int B, int H, int64_t N, int D, int dtype,
+                moa_stream_t stream) {
+  using namespace moa;
+  MOA_REQUIRE(q && k && cos_t && sin_t, "rope_qk: null pointer");
+  MOA_REQUIRE(B > 0 && H > 0 && N > 0, "rope_qk: bad shape");
+  MOA_REQUIRE(sb % 8 == 0 && sh % 8 == 0 && sn % 8 == 0 && cos_batch_stride % 8 == 0 && cos_token_stride % 8 == 0,
+              "rope_qk: strides must be multiples of 8 elements");
+  MOA_REQUIRE((int64_t)B * H * N < (1ll << 40), "rope_qk: too many rows");
+  if (dtype == MOA_F16)
+    return launch_rope<__half>(q, k, sb, sh, sn, cos_t, sin_t, cos_batch_stride, cos_token_stride, B, H, N, D,
+                               (cudaStream_t)stream);
+  if (dtype == MOA_BF16)
+    return launch_rope<__nv_bfloat16>(q, k, sb, sh, sn, cos_t, sin_t, cos_batch_stride, cos_token_stride, B, H, N, D,
+                                      (cudaStream_t)stream);
+  set_error_text("rope_qk: dtype must be MOA_F16 or MOA_BF16");
+  return MOA_ERR_UNSUPPORTED;
+}
 
 int moa_cache_append(void* k_cache, void* v_cache, const void* k_new, const void* v_new, int64_t new_batch_stride,
                      int64_t new_head_stride, const int64_t* head_start, int64_t* valid_len, int64_t* update_index,

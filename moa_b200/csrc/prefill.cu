@@ -153,13 +153,14 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Bounded wait.  Returns false when the block is aborting (this wait or another one gave up).
 // The limit is counted with clock64 (a cheap per-SM counter); reading %globaltimer costs far more
 // than a typical wait lasts and must stay off this path.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, Ctl* ctl, int32_t* status, int code,
+                                            long long limit_cycles = kWaitLimitCycles) {
   const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0) {
       if (*(volatile int*)&ctl->abort) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *(volatile int*)&ctl->abort = 1;
         if (atomicCAS(&status[0], 0, code) == 0) {
           status[1] = (int32_t)blockIdx.x;
@@ -676,6 +677,20 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
+// Self-test of the bounded wait: one thread waits, with a short limit, on a barrier nobody arrives at.
+// The wait must give up, set the abort flag and leave its code in the status words; the kernel then
+// returns normally and the context stays usable.
+__global__ void wait_selftest_kernel(int32_t* status, long long limit_cycles) {
+  __shared__ Ctl ctl;
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl.q_full, 1);
+    ctl.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool ok = mbar_try_wait(&ctl.q_full, 0) || mbar_wait_slow(&ctl.q_full, 0, &ctl, status, kWaitQ, limit_cycles);
+    if (ok) status[0] = -1;  // cannot happen: nothing arrives on the barrier
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -780,4 +795,13 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   }
   return out_f32 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, grid, st)
                  : launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, grid, st);
+}
+
+extern "C" int moa_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, moa_stream_t stream) {
+  using namespace moa;
+  MOA_REQUIRE(status != nullptr, "selftest: null status");
+  MOA_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, "selftest: limit must be within (0, 2e9] cycles");
+  wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (long long)limit_cycles);
+  MOA_CUDA_CHECK(cudaGetLastError());
+  return MOA_OK;
 }

@@ -42,13 +42,21 @@ def rotary_cos_sin(position_ids: Tensor, head_dim: int, theta: float, dtype: tor
 
 
 def apply_rotary_pos_emb(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> Tuple[Tensor, Tensor]:
-    """q, k (B, H, q_len, D); cos, sin (B, q_len, D)."""
-    def rot(x):
-        d = x.shape[-1]
-        return torch.cat([-x[..., d // 2:], x[..., : d // 2]], dim=-1)
+    """Rotary embedding of q and k, in place, in one kernel pass (``moa_rope_qk``).  q, k ``(B, H, q_len, D)``
+    with the same strides and a contiguous last dim; cos, sin ``(B, q_len, D)`` (or ``(1, q_len, D)``) in their
+    dtype.  Returns ``(q, k)`` (the same tensors)."""
+    from . import _lib
 
-    cos, sin = cos[:, None], sin[:, None]
-    return q * cos + rot(q) * sin, k * cos + rot(k) * sin
+    B, H, N, D = q.shape
+    assert k.shape == q.shape and q.stride() == k.stride() and q.stride(-1) == 1
+    assert cos.shape[-2:] == (N, D) and cos.stride() == sin.stride() and cos.stride(-1) == 1 and cos.dtype == q.dtype
+    assert cos.shape[0] in (1, B)
+    cs_b = 0 if cos.shape[0] == 1 else cos.stride(0)
+    with torch.cuda.device(q.device):
+        _lib.check("moa_rope_qk", _lib.lib.moa_rope_qk(
+            q.data_ptr(), k.data_ptr(), q.stride(0), q.stride(1), q.stride(2), cos.data_ptr(), sin.data_ptr(),
+            cs_b, cos.stride(1), B, H, N, D, _lib.dtype_code(q.dtype), _lib.current_stream(q.device)))
+    return q, k
 
 
 class MoAAttention(nn.Module):

@@ -118,3 +118,27 @@ def test_head_sharded_attention_on_one_gpu_equals_unsharded():
     # the shards cut the flattened cache into different chunks, so partial sums are grouped differently:
     # equal up to the rounding of the fp16 store
     assert (got.float() - ref.float()).abs().max() <= 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Dh", [128, 64])
+def test_rope_kernel_matches_fp32_rotation_rounded_once(dtype, Dh):
+    from moa_b200.module import apply_rotary_pos_emb, rotary_cos_sin
+    gen = torch.Generator().manual_seed(5)
+    B, H, N = 2, 3, 77
+    # (B, N, H, D) storage viewed as (B, H, N, D), as the projections produce it
+    q = torch.randn(B, N, H, Dh, generator=gen).to(dtype).cuda().transpose(1, 2)
+    k = torch.randn(B, N, H, Dh, generator=gen).to(dtype).cuda().transpose(1, 2)
+    pos = torch.stack([torch.arange(N), torch.arange(N) + 60000]).cuda()
+    cos, sin = rotary_cos_sin(pos, Dh, 500000.0, dtype)
+    want_q = orc.apply_rope(q.float().cpu(), cos.float().cpu(), sin.float().cpu()).to(dtype)
+    want_k = orc.apply_rope(k.float().cpu(), cos.float().cpu(), sin.float().cpu()).to(dtype)
+    q2, k2 = apply_rotary_pos_emb(q, k, cos, sin)
+    assert q2 is q and k2 is k
+    assert torch.equal(q.cpu(), want_q) and torch.equal(k.cpu(), want_k)
+    # one shared table for all batch rows
+    q3 = torch.randn(B, H, N, Dh, generator=gen).to(dtype).cuda()
+    k3 = q3.clone()
+    want = orc.apply_rope(q3.float().cpu(), cos[:1].float().cpu(), sin[:1].float().cpu()).to(dtype)
+    apply_rotary_pos_emb(q3, k3, cos[:1], sin[:1])
+    assert torch.equal(q3.cpu(), want) and torch.equal(k3.cpu(), want)

@@ -192,3 +192,21 @@ def test_short_prompt_without_sizes_is_dense_causal():
     moa_b200.check_device_status()
     ref = orc.prefill_attention_fp32(q, k, v, 0.1, [0, 0], [1, 1])
     _close(out, ref, "dense causal N=40")
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
+    """Failure detection without a fault: a bounded wait on a barrier nobody signals gives up after its
+    limit, the status words carry the code, check_device_status raises, and the next launch works."""
+    from moa_b200 import _lib
+    from moa_b200.attention import _status_words
+    st = _status_words("cuda:0")
+    st.zero_()
+    rc = _lib.lib.moa_selftest_bounded_wait(st.data_ptr(), 20_000_000, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    with pytest.raises(moa_b200.MoaError, match="wait"):
+        moa_b200.check_device_status("cuda:0")
+    assert st.tolist() == [0, 0, 0, 0]            # cleared by the check
+    gen = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(1, 1, 128, 128, generator=gen).half() for _ in range(3))
+    out = _run(q, k, v, 0.1, [1], [1])            # the context is alive and the kernel still right
+    _close(out, orc.prefill_attention_fp32(q, k, v, 0.1, [1], [1]), "after the timed-out wait")
