@@ -159,7 +159,7 @@ int moa_cache_fill(const void* k, const void* v, int64_t sb, int64_t sh, int64_t
  * 473-696): q-block bi (64 rows) sees kv-block j iff j <= bi and (j < sink_blocks[h] or
  * j >= bi + 1 - local_blocks[h]); inside a block the mask is causal.
  *
- *   q, k, v  (B, H, N, D) with byte-aligned element strides (sb, sh, sn), D contiguous,
+ *   q, k, v  (B, H, N, D), D = 64 or 128, with element strides (sb, sh, sn), D contiguous,
  *            every stride a multiple of 8 elements, base pointers 16-byte aligned
  *   out      written as out[b*ob + n*on + h*oh + d]; (B,N,H,D) contiguous is ob=N*H*D, on=H*D, oh=D
  *   sink_blocks, local_blocks (H) int32 device arrays, in 64-token blocks

@@ -44,7 +44,7 @@
 namespace moa {
 namespace {
 
-constexpr int kD = 128;            // head_dim this kernel is built for
+constexpr int kD = 128;            // largest head_dim (shared-memory and TMEM layout are sized for it; 64 uses half)
 constexpr int kBM = 128;           // query rows per tile (two tiles per block)
 constexpr int kBN = 64;            // KV tokens per tile (= the mask's block size)
 constexpr int kStages = 4;         // depth of the K ring and of the V ring (power of two)
@@ -297,7 +297,9 @@ __device__ __forceinline__ TileSeen tile_seen(bool exists, int t, const TileBloc
   return r;
 }
 
-template <typename T, bool OUT_F32>
+// DH = head_dim, 64 or 128.  The shared-memory and TMEM layout is the one of 128; with 64 only the first
+// 64-column panel of every Q/K/V tile and the first 64 O columns are used.
+template <typename T, bool OUT_F32, int DH>
 __global__ void __launch_bounds__(kThreads, 1)
 moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
@@ -320,6 +322,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const TileBlocks tb = tile_blocks(t0, active1 ? t1 : t0, nb, sink_b, local_b);
   const int nkv = tb.count();
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr int NH = DH / 64;                 // 64-column panels per tile
+  constexpr int kQPanel = kBM * 128, kKPanel = kBN * 128;   // bytes of one panel
+  static_assert(DH == 64 || DH == 128, "head_dim");
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
@@ -355,11 +360,12 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctl->q_full, 2 * kQBytes);
-      tma_load_4d(smem + kSmemQ, &map_q, &ctl->q_full, 0, t0 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes / 2, &map_q, &ctl->q_full, 64, t0 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes, &map_q, &ctl->q_full, 0, t1 * kBM, h, b);
-      tma_load_4d(smem + kSmemQ + kQBytes + kQBytes / 2, &map_q, &ctl->q_full, 64, t1 * kBM, h, b);
+      mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        tma_load_4d(smem + kSmemQ + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, t0 * kBM, h, b);
+        tma_load_4d(smem + kSmemQ + kQBytes + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, t1 * kBM, h, b);
+      }
       int k_issued = 0, v_issued = 0;
       bool ok = true;
       // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
@@ -373,9 +379,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (!ok) break;
           uint8_t* dst = smem + kSmemK + s * kKBytes;
           const int row = tb.block(u) * kBN;
-          mbar_expect_tx(&ctl->k_full[s], kKBytes);
-          tma_load_4d(dst, &map_k, &ctl->k_full[s], 0, row, h, b);
-          tma_load_4d(dst + kKBytes / 2, &map_k, &ctl->k_full[s], 64, row, h, b);
+          mbar_expect_tx(&ctl->k_full[s], NH * kKPanel);
+#pragma unroll
+          for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_k, &ctl->k_full[s], 64 * hf, row, h, b);
           k_issued = u + 1;
         }
         if (u >= 1) {
@@ -386,9 +392,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (!ok) break;
           uint8_t* dst = smem + kSmemV + s * kKBytes;
           const int row = tb.block(uv) * kBN;
-          mbar_expect_tx(&ctl->v_full[s], kKBytes);
-          tma_load_4d(dst, &map_v, &ctl->v_full[s], 0, row, h, b);
-          tma_load_4d(dst + kKBytes / 2, &map_v, &ctl->v_full[s], 64, row, h, b);
+          mbar_expect_tx(&ctl->v_full[s], NH * kKPanel);
+#pragma unroll
+          for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_v, &ctl->v_full[s], 64 * hf, row, h, b);
           v_issued = uv + 1;
         }
       }
@@ -415,7 +421,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const int x = warp - 9;
       const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
-      constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, kD);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, DH);
       // descriptors differ only in their start-address field (bytes >> 4): build each base once
       const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
@@ -447,7 +453,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
+        for (int kk = 0; kk < DH / 16; ++kk) {
           // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
           const uint32_t half = kk >> 2, off = (kk & 3) * 32;
           if (!(MOA_PREFILL_DBG & 4))
@@ -613,7 +619,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       else if (pk[3] == 0x12345678u) l += 1.f;
       if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < kD; c0 += 32) {
+        for (int c0 = 0; c0 < DH; c0 += 32) {
           uint32_t ov[32];
           tmem_ld32(lane_base + col_o(x) + c0, ov);
           tmem_wait_ld();
@@ -640,7 +646,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
                       ((int64_t)b * p.o_sb + i_tok * p.o_sn + (int64_t)h * p.o_sh) * (OUT_F32 ? 4 : 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kD; c0 += 32) {
+      for (int c0 = 0; c0 < DH; c0 += 32) {
         uint32_t ov[32];
         tmem_ld32(lane_base + col_o(x) + c0, ov);
         tmem_wait_ld();
@@ -710,14 +716,14 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // (B, H, N, D) tensor with element strides (sb, sh, sn, 1) -> 4-d map (D, N, H, B), box (64, rows, 1, 1)
-int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_t N, int64_t sb, int64_t sh,
+int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_t N, int D, int64_t sb, int64_t sh,
              int64_t sn, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_error_text("prefill: cuTensorMapEncodeTiled entry point not available");
     return MOA_ERR_CUDA;
   }
-  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
   const cuuint64_t strides[3] = {(cuuint64_t)sn * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
   const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -731,10 +737,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_
   return MOA_OK;
 }
 
-template <typename T, bool F32>
+template <typename T, bool F32, int DH>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
                    dim3 grid, cudaStream_t stream) {
-  auto kern = moa_prefill_kernel<T, F32>;
+  auto kern = moa_prefill_kernel<T, F32, DH>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     MOA_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
@@ -759,8 +765,8 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   MOA_REQUIRE((N + 255) / 256 < 148 || H <= 65535, "prefill: too many heads for one launch");
   MOA_REQUIRE(N < (1LL << 31) - 512, "prefill: sequence too long");
   MOA_REQUIRE(sm_scale > 0.f, "prefill: sm_scale must be positive");
-  if (D != kD) {
-    set_error_text("prefill: head_dim must be 128");
+  if (D != 64 && D != 128) {
+    set_error_text("prefill: head_dim must be 64 or 128");
     return MOA_ERR_UNSUPPORTED;
   }
   if (dtype != MOA_F16 && dtype != MOA_BF16) {
@@ -775,26 +781,31 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   MOA_REQUIRE(o_sb % 8 == 0 && o_sn % 8 == 0 && o_sh % 8 == 0, "prefill: out strides must be multiples of 8 elements");
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_map(&mq, q, dtype, B, H, N, q_sb, q_sh, q_sn, kBM)) != MOA_OK) return rc;
-  if ((rc = make_map(&mk, k, dtype, B, H, N, k_sb, k_sh, k_sn, kBN)) != MOA_OK) return rc;
-  if ((rc = make_map(&mv, v, dtype, B, H, N, v_sb, v_sh, v_sn, kBN)) != MOA_OK) return rc;
+  if ((rc = make_map(&mq, q, dtype, B, H, N, D, q_sb, q_sh, q_sn, kBM)) != MOA_OK) return rc;
+  if ((rc = make_map(&mk, k, dtype, B, H, N, D, k_sb, k_sh, k_sn, kBN)) != MOA_OK) return rc;
+  if ((rc = make_map(&mv, v, dtype, B, H, N, D, v_sb, v_sh, v_sn, kBN)) != MOA_OK) return rc;
   PrefillParams p;
   p.out = out; p.o_sb = o_sb; p.o_sn = o_sn; p.o_sh = o_sh;
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   const int nsuper = (int)((N + 2 * kBM - 1) / (2 * kBM));
   // fewer super-tiles per head than SMs, and all of K and V fits in L2 with room to spare: interleave the heads
-  const int64_t kv_bytes = (int64_t)B * H * N * kD * 2 * 2;
+  const int64_t kv_bytes = (int64_t)B * H * N * D * 2 * 2;
   p.heads_fastest = (nsuper < 148 && H <= 65535 && kv_bytes <= (64ll << 20)) ? 1 : 0;
   dim3 grid = p.heads_fastest ? dim3((unsigned)H, (unsigned)nsuper, (unsigned)B)
                               : dim3((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == MOA_F16) {
-    return out_f32 ? launch_prefill<__half, true>(mq, mk, mv, p, grid, st)
-                   : launch_prefill<__half, false>(mq, mk, mv, p, grid, st);
+  const int variant = (dtype == MOA_BF16 ? 4 : 0) + (out_f32 ? 2 : 0) + (D == 64 ? 1 : 0);
+  switch (variant) {
+    case 0: return launch_prefill<__half, false, 128>(mq, mk, mv, p, grid, st);
+    case 1: return launch_prefill<__half, false, 64>(mq, mk, mv, p, grid, st);
+    case 2: return launch_prefill<__half, true, 128>(mq, mk, mv, p, grid, st);
+    case 3: return launch_prefill<__half, true, 64>(mq, mk, mv, p, grid, st);
+    case 4: return launch_prefill<__nv_bfloat16, false, 128>(mq, mk, mv, p, grid, st);
+    case 5: return launch_prefill<__nv_bfloat16, false, 64>(mq, mk, mv, p, grid, st);
+    case 6: return launch_prefill<__nv_bfloat16, true, 128>(mq, mk, mv, p, grid, st);
+    default: return launch_prefill<__nv_bfloat16, true, 64>(mq, mk, mv, p, grid, st);
   }
-  return out_f32 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, grid, st)
-                 : launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, grid, st);
 }
 
 extern "C" int moa_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, moa_stream_t stream) {

@@ -210,3 +210,23 @@ def test_a_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
     q, k, v = (torch.randn(1, 1, 128, 128, generator=gen).half() for _ in range(3))
     out = _run(q, k, v, 0.1, [1], [1])            # the context is alive and the kernel still right
     _close(out, orc.prefill_attention_fp32(q, k, v, 0.1, [1], [1]), "after the timed-out wait")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_64(dtype):
+    """Llama-3.2-1B has 64-wide heads (one of the reference's example plans)."""
+    gen = torch.Generator().manual_seed(64)
+    B, H, N = 2, 3, 700
+    q, k, v = (torch.randn(B, H, N, 64, generator=gen).to(dtype) for _ in range(3))
+    sm = 64 ** -0.5
+    sink_b, local_b = [1, 1, 2], [1, 4, 9]
+    ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b)
+    if dtype == torch.float16:
+        out = _run(q, k, v, sm, sink_b, local_b)
+        assert out.shape == (B, N, H, 64)
+        _close(out, ref, "D=64 fp16")
+    else:
+        out32 = _run(q, k, v, sm, sink_b, local_b, out_dtype=torch.float32)
+        _close(out32, ref, "D=64 bf16, fp32 store", 8e-3, 4e-3)
+        out16 = _run(q, k, v, sm, sink_b, local_b)
+        assert torch.equal(out16.cpu(), out32.cpu().bfloat16())
