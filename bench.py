@@ -10,7 +10,8 @@ caches filled from a 16k-token random sequence, then decode steps with one new t
 sequence.  A "step" is one fused decode launch (ring append + flash-decoding + bookkeeping)
 over one batch.  `value` is decode tokens/s with the step inputs resident in HBM; `e2e` is the
 same loop through the public API with the step's q/k/v coming from pinned host memory and
-the step's output copied back.  The K/V working set (about 0.55 GB at the default seed) is larger
+the step's output copied back (copies double-buffered on their own streams, so they overlap the
+neighbouring steps' kernels).  The K/V working set (about 0.55 GB at the default seed) is larger
 than L2 (126 MB), so no L2 flush is needed between steps.
 
 With N > 1 (torchrun) every rank owns the ring caches of one 32-head shard (heads, or equally
@@ -193,8 +194,9 @@ def build_cache(caps, device, seed, fill_tokens):
     return cache, gen
 
 
-def time_region(fn, steps, device, dist):
-    """barrier + sync, CUDA events on the launching stream around exactly `steps` calls, max over ranks."""
+def time_region(fn, steps, device, dist, drain=None):
+    """barrier + sync, CUDA events on the launching stream around exactly `steps` calls, max over ranks.
+    `drain` makes the launching stream wait for work the steps put on other streams before the end event."""
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize(device)
@@ -203,6 +205,8 @@ def time_region(fn, steps, device, dist):
     e0.record()
     for i in range(steps):
         fn(i)
+    if drain is not None:
+        drain()
     e1.record()
     torch.cuda.synchronize(device)
     w1 = time.time()
@@ -374,15 +378,42 @@ def run_gpu(args):
         cache.decode_attention(q, k, v, 0, sm, out=out)
 
     # end-to-end: q/k/v of the step come from pinned host memory, the output goes back to it
-    # (the host keeps q, k, v of a step packed in one pinned buffer, so a step costs one copy each way)
+    # (the host keeps q, k, v of a step packed in one pinned buffer, so a step costs one copy each way;
+    # the copies run on their own streams, double-buffered, so that the upload of step i+1 and the
+    # download of step i-1 overlap the kernel of step i — every step still uploads its inputs and downloads
+    # its output inside the timed region)
     host_in = [torch.stack([t.cpu() for t in trio]).pin_memory() for trio in pool]
-    dev_in = torch.empty(3, B, H, 1, D, dtype=torch.float16, device=device)
-    host_out = torch.empty(B, 1, H, D, dtype=torch.float16).pin_memory()
+    dev_in = [torch.empty(3, B, H, 1, D, dtype=torch.float16, device=device) for _ in range(2)]
+    dev_out = [torch.empty(B, 1, H, D, dtype=torch.float16, device=device) for _ in range(2)]
+    host_out = [torch.empty(B, 1, H, D, dtype=torch.float16).pin_memory() for _ in range(2)]
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_ready = [torch.cuda.Event() for _ in range(2)]
+    out_free = [torch.cuda.Event() for _ in range(2)]
+    main = torch.cuda.current_stream(device)
+    for ev in in_free + out_free:
+        ev.record(main)
 
     def step_e2e(i):
-        dev_in.copy_(host_in[i % n_pool], non_blocking=True)
-        cache.decode_attention(dev_in[0], dev_in[1], dev_in[2], 0, sm, out=out)
-        host_out.copy_(out, non_blocking=True)
+        s = i & 1
+        with torch.cuda.stream(up):
+            up.wait_event(in_free[s])
+            dev_in[s].copy_(host_in[i % n_pool], non_blocking=True)
+            in_ready[s].record(up)
+        main.wait_event(in_ready[s])
+        main.wait_event(out_free[s])
+        cache.decode_attention(dev_in[s][0], dev_in[s][1], dev_in[s][2], 0, sm, out=dev_out[s])
+        in_free[s].record(main)
+        out_ready[s].record(main)
+        with torch.cuda.stream(down):
+            down.wait_event(out_ready[s])
+            host_out[s].copy_(dev_out[s], non_blocking=True)
+            out_free[s].record(down)
+
+    def e2e_drain():
+        main.wait_stream(up)
+        main.wait_stream(down)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     warm = max(args.warmup, 3)
@@ -391,7 +422,8 @@ def run_gpu(args):
     ms, win1 = time_region(step_resident, args.steps, device, dist)
     for i in range(warm):
         step_e2e(i)
-    ms_e2e, win2 = time_region(step_e2e, args.steps, device, dist)
+    e2e_drain()
+    ms_e2e, win2 = time_region(step_e2e, args.steps, device, dist, drain=e2e_drain)
 
     hbm_peak, tf_peak, which = measured_peaks()
     prefill = prefill_leg(device, tf_peak, which, args.prefill_n) if (world == 1 and not args.no_prefill) else None

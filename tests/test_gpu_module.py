@@ -142,3 +142,47 @@ def test_rope_kernel_matches_fp32_rotation_rounded_once(dtype, Dh):
     want = orc.apply_rope(q3.float().cpu(), cos[:1].float().cpu(), sin[:1].float().cpu()).to(dtype)
     apply_rotary_pos_emb(q3, k3, cos[:1], sin[:1])
     assert torch.equal(q3.cpu(), want) and torch.equal(k3.cpu(), want)
+
+
+def test_real_example_plan_prefill_then_decode():
+    """A layer of the reference's own vicuna-7b plan (examples/lmsys--vicuna-7b-v1.5-16k, recorded in the
+    cache_config fixture): sizes through moa_config_to_cache_config, heads permuted as permute_head does,
+    sparse prefill of a 2048-token prompt, ring fill, then fused decode steps — all against the oracle."""
+    import json
+    import os
+    cases = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "cache_config.json")))
+    case = next(c for c in cases if c["model"].startswith("lmsys--vicuna-7b"))
+    plan = {"alphas": case["plan"]["alphas"][1:2], "betas": case["plan"]["betas"][1:2]}
+    perm = moa_b200.moa_config_to_permutation(plan)[0][0].tolist()
+    plan = {"alphas": [[plan["alphas"][0][i] for i in perm]], "betas": [[plan["betas"][0][i] for i in perm]]}
+    N, B, D = 2048, 1, 128
+    cfg = moa_b200.moa_config_to_cache_config(plan, N, 64, verbose=False)
+    assert cfg == orc.cache_config(plan, N, 64)
+    caps, static = cfg["cache_size"][0], cfg["static_size"][0]
+    H = len(caps)
+    assert caps == sorted(caps) or len(set(caps)) <= 4          # equal capacities end up adjacent
+    gen = torch.Generator().manual_seed(42)
+    q, k, v = (torch.randn(B, H, N, D, generator=gen).half() for _ in range(3))
+    cache = moa_b200.StaticCircularCache([caps], B, D, [static], "cuda", torch.float16)
+    ocache = orc.RingCacheOracle([caps], [static], B, D, dtype=np.float16)
+    kd, vd = k.cuda(), v.cuda()
+    cache.update(kd, vd, 0)
+    ocache.update(k.numpy(), v.numpy(), 0)
+    out = moa_b200.mixture_of_sparse_attention(q.cuda(), kd, vd, D ** -0.5, sink_size=cache.static_cache_size[0],
+                                               local_size=cache.circular_cache_size[0])
+    moa_b200.check_device_status()
+    ref = orc.prefill_attention_fp32(q, k, v, D ** -0.5, [s // 64 for s in static],
+                                     [(c - s) // 64 for c, s in zip(caps, static)])
+    a, r = _rel(out, ref)
+    assert a < 2e-3 and r < 1e-3, (a, r)
+    assert np.array_equal(cache.key_cache[0].cpu().numpy(), ocache.key_cache[0])
+    for step in range(3):
+        q1, k1, v1 = (torch.randn(B, H, 1, D, generator=gen).half() for _ in range(3))
+        kc, vc = ocache.update(k1.numpy(), v1.numpy(), 0)
+        o1 = cache.decode_attention(q1.cuda(), k1.cuda(), v1.cuda(), 0, D ** -0.5)
+        r1 = orc.decode_attention_fp32(q1, torch.from_numpy(kc), torch.from_numpy(vc),
+                                       torch.from_numpy(ocache.cache_head_start_index[0]),
+                                       torch.from_numpy(ocache.cache_valid_length[0]), D ** -0.5)
+        a, r = _rel(o1, r1)
+        assert a < 2e-3 and r < 1e-3, (step, a, r)
+    assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), ocache.cache_update_index[0])
