@@ -1,26 +1,27 @@
 // Block-sparse causal prefill (attention sink + per-head sliding window) on tcgen05 / TMEM / TMA.
 //
 // One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
-// A and B that share every K/V chunk brought into shared memory.  A step covers a chunk of 128 KV
-// tokens (two of the mask's 64-token blocks): the 128 x 128 x 16 MMA runs at the tensor core's full
-// rate, the 128 x 64 x 16 one does not (46 instead of 32 cycles, measured).  Roles:
+// A and B that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
-//              tile (= TMEM lane r).  Per chunk it loads its S row from TMEM, computes the
+//              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM and at once hands
+//              the S columns back (so the tensor core can start the tile's next S), computes the
 //              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
-//              column) over the first half of the S columns, rescales O in TMEM when the max
-//              moved, and finally runs the epilogue
-//   warp  8    TMA producer (one lane): both Q tiles once, then K and V chunks through two rings
-//              of shared-memory stages
+//              column) to the tile's P columns in TMEM, rescales O in TMEM when the max moved,
+//              and finally runs the epilogue
+//   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
+//              two rings of shared-memory stages
 //   warp  9,10 MMA issuers of tile A and tile B (one lane each; warp 9 owns the TMEM allocation):
-//              S = Q K^T (M128 N128 K=head_dim, Q and K from shared memory), O += P V (M128
-//              N=head_dim K128, P from TMEM, V from shared memory as an MN-major operand).
-// Per tile the order on the tensor core is S(0), then for every step i: [softmax turns S(i) into
-// P(i)] -> O += P(i) V(i) -> S(i+1).  MMAs of one issuing thread execute in order, so S(i+1) may
-// overwrite the columns P(i) was read from without a barrier, and "S(i+1) is complete" also tells
-// the softmax threads that O is no longer being accumulated into.  While one tile's softmax runs,
-// the tensor core works on the other tile: the two tiles settle into opposite phases.
-// Only the chunks inside "sink U band" of the super-tile are loaded; a tile skips the chunks only
-// the other tile sees, and only the (at most four) edge chunks of a tile get an element mask.
+//              S = Q K^T (M128 N64 K128, Q and K from shared memory), O += P V (M128 N128 K64,
+//              P from TMEM, V from shared memory as an MN-major operand).  An issuer is a single
+//              thread that competes for issue slots with the softmax warps of its scheduler, so
+//              its loop is kept to a few dozen instructions per step: the KV blocks a tile takes
+//              part in are two index ranges in closed form, and ring stages are handed back with
+//              plain mbarrier arrives wherever completion is already known.
+// Per tile the order is S(i) -> [softmax loads S(i)] -> S(i+1) may start -> [softmax writes P(i)]
+// -> O += P(i) V(i): the next S is computed while the exponentials of the current one run, and
+// the two tiles interleave on the tensor core.  Only the 64-token KV blocks inside "sink U band"
+// of the super-tile are loaded; a tile skips the blocks only the other tile sees, and only the
+// (at most three) edge blocks of a tile get an element mask.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -28,6 +29,11 @@
 //
 // Every wait on an mbarrier is bounded: when it runs out the block sets an abort flag, records a
 // code in the status words, drains, frees its TMEM and returns.
+// Development probes (never compiled into the library): MOA_PREFILL_DBG bit 1 skips the softmax
+// threads' TMEM traffic, bit 2 skips the MMAs themselves (barrier handshakes only).
+#ifndef MOA_PREFILL_DBG
+#define MOA_PREFILL_DBG 0
+#endif
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -40,59 +46,67 @@ namespace {
 
 constexpr int kD = 128;            // largest head_dim (shared-memory and TMEM layout are sized for it; 64 uses half)
 constexpr int kBM = 128;           // query rows per tile (two tiles per block)
-constexpr int kBlk = 64;           // the mask's block size
-constexpr int kBN = 128;           // KV tokens per step: a chunk of two mask blocks, so that S = Q K^T runs with N = 128
-constexpr int kKStages = 3;        // depth of the K ring (chunks)
-constexpr int kVStages = 2;        // depth of the V ring
+constexpr int kBN = 64;            // KV tokens per tile (= the mask's block size)
+constexpr int kStages = 4;         // depth of the K ring and of the V ring (power of two)
 constexpr int kSoftmaxThreads = 128;  // per tile
 constexpr int kThreads = 352;
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns: O_A [0,128) O_B [128,256), S_A [256,384) S_B [384,512).  P (two 16-bit values per column)
-// overwrites columns [0,64) of its tile's S once the S row is in registers.
+// TMEM columns: O_A [0,128) O_B [128,256), S_A [256,320) S_B [320,384), P_A [384,416) P_B [416,448)
 __host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
-__host__ __device__ constexpr uint32_t col_s(int x) { return 256u + (uint32_t)x * 128u; }
+__host__ __device__ constexpr uint32_t col_s(int x) { return 256u + (uint32_t)x * 64u; }
+__host__ __device__ constexpr uint32_t col_p(int x) { return 384u + (uint32_t)x * 32u; }
 
-constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per Q tile (two 16 KiB panels: dims 0-63, 64-127)
-constexpr int kKBytes = kBN * kD * 2;       // 32 KiB per K or V chunk (two 16 KiB panels)
+constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per Q tile (two 16 KiB halves: dims 0-63, 64-127)
+constexpr int kKBytes = kBN * kD * 2;       // 16 KiB per K or V tile (two 8 KiB halves)
 constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + 2 * kQBytes;
-constexpr int kSmemV = kSmemK + kKStages * kKBytes;
-constexpr int kSmemCtl = kSmemV + kVStages * kKBytes;
+constexpr int kSmemV = kSmemK + kStages * kKBytes;
+constexpr int kSmemCtl = kSmemV + kStages * kKBytes;
 constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
-static_assert(kSmemBytes <= 227 * 1024, "shared memory per block");
 
-// the running max is only moved when a chunk exceeds it by more than this (log2 units)
+// the running max is only moved when a block exceeds it by more than this (log2 units)
 constexpr float kLazyMaxSlack = 8.f;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock: far above any legitimate wait
 constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drain loops of the abort path
 
 // status codes written to status[0] when a wait gives up
-enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitO = 7, kWaitVFull = 8, kWaitVEmpty = 9,
-       kWaitLock = 11 };
+enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
+       kWaitVFull = 8, kWaitVEmpty = 9, kWaitSFree = 10 };
 
 struct Ctl {
   uint64_t q_full;
-  uint64_t k_full[kKStages];
-  uint64_t v_full[kVStages];
-  uint64_t k_empty[2][kKStages];  // [tile]: that tile is done with the K stage
-  uint64_t v_empty[2][kVStages];
-  uint64_t s_full[2];   // [tile] tensor core -> softmax: S is in TMEM (and every earlier MMA of the tile has finished)
+  uint64_t k_full[kStages];
+  uint64_t v_full[kStages];
+  uint64_t k_empty[2][kStages];  // [tile]: that tile is done with the K stage
+  uint64_t v_empty[2][kStages];
+  uint64_t s_full[2];   // [tile] tensor core -> softmax: S is in TMEM
+  uint64_t s_free[2];   // [tile] softmax -> issuer: S has been read, its columns may be overwritten
   uint64_t p_full[2];   // [tile] softmax -> issuer: P is in TMEM (and O rescaled)
+  uint64_t pv_done[2];  // [tile] tensor core -> softmax: O += P V finished (P columns free, O may be touched)
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
-  int pipe_lock;   // held by the issuer whose batch of MMAs is being queued
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
 
-#ifdef MOA_PREFILL_TRACE   // development probe (never compiled into the library): time stamps of one block's first 64 steps
-#define TRACE_EV(role, step, ev)                                                                     \
-  do {                                                                                               \
-    if (blockIdx.x == MOA_PREFILL_TRACE && blockIdx.y == 5 && (step) < 64)                           \
-      reinterpret_cast<long long*>(p.status)[256 + (((role) * 64 + (step)) * 8 + (ev))] = clock64(); \
+#ifdef MOA_PREFILL_PROFILE
+#define PROF_DECL long long _pt = clock64(); long long _pa[16] = {0}; const int _pbase = 0;
+#define PROF_ADD(slot, cond)                     \
+  do {                                           \
+    long long _now = clock64();                  \
+    _pa[(slot) % 16 + 0 * _pbase] += _now - _pt;  \
+    _pt = _now;                                  \
+  } while (0)
+#define PROF_FLUSH(base, cond)                                                                        \
+  do {                                                                                                \
+    if (cond)                                                                                         \
+      for (int _i = 0; _i < 16; ++_i)                                                                 \
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (base) + _i, (unsigned long long)_pa[_i]); \
   } while (0)
 #else
-#define TRACE_EV(role, step, ev)
+#define PROF_DECL
+#define PROF_ADD(slot, cond)
+#define PROF_FLUSH(base, cond)
 #endif
 
 struct PrefillParams {
@@ -163,41 +177,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* c
   return mbar_wait_slow(bar, parity, ctl, status, code);
 }
 
-// One lane of a converged warp (the lowest active one).
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "elect.sync _|P, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
-// The two issuers take turns on the tensor core: a tile's batch (O += P V, then the next S) is queued as a
-// whole, so that its S is complete as early as possible and the tiles settle into opposite phases (one in
-// its softmax while the other's MMAs run).  Bounded like every other wait.
-__device__ __forceinline__ bool pipe_acquire(Ctl* ctl, int32_t* status) {
-  const long long t0 = clock64();
-  for (uint32_t spin = 1; atomicCAS(&ctl->pipe_lock, 0, 1) != 0; ++spin) {
-    __nanosleep(32);
-    if ((spin & 255u) == 0) {
-      if (*(volatile int*)&ctl->abort) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *(volatile int*)&ctl->abort = 1;
-        if (atomicCAS(&status[0], 0, kWaitLock) == 0) {
-          status[1] = (int32_t)blockIdx.x;
-          status[2] = (int32_t)(blockIdx.y + 65536 * blockIdx.z);
-          status[3] = (int32_t)threadIdx.x;
-        }
-        return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void pipe_release(Ctl* ctl) { atomicExch(&ctl->pipe_lock, 0); }
-
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2, int c3) {
   asm volatile(
@@ -243,59 +222,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// Two fp32 values in one 64-bit register pair, for the packed fp32 instructions of sm_100 (one issue
-// slot for two lanes' worth of work).
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add_down(uint64_t a, uint64_t b) {   // rounds towards -infinity
-  uint64_t d;
-  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-
-// 2^x for a pair of arguments x <= 8 or so, on the FMA pipe instead of the special-function unit:
-// n = floor(x) by a round-down addition of 1.5 * 2^23, f = x - n in [0, 1), 2^f by a cubic fitted to
-// it (largest relative error 7.5e-5, well below the rounding of P to 16 bits), and n added into the
-// exponent field.  Arguments are clamped at -125 (masked keys are -inf): the cubic can be a little
-// below 1, and its exponent field must not be taken below zero.
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  f2_unpack(x2, x0, x1);
-  x2 = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-  const uint64_t magic = f2_pack(12582912.f, 12582912.f), neg_magic = f2_pack(-12582912.f, -12582912.f);
-  const uint64_t r2 = f2_add_down(x2, magic);                         // mantissa bits now hold floor(x)
-  const uint64_t n2 = f2_add(r2, neg_magic);                          // floor(x) as a float
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);            // fractional part
-  uint64_t q2 = f2_fma(f2, f2_pack(0.078023538f, 0.078023538f), f2_pack(0.226066232f, 0.226066232f));
-  q2 = f2_fma(q2, f2, f2_pack(0.695835173f, 0.695835173f));
-  q2 = f2_fma(q2, f2, f2_pack(0.999924898f, 0.999924898f));
-  float q0, q1, r0, r1;
-  f2_unpack(q2, q0, q1);
-  f2_unpack(r2, r0, r1);
-  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
-}
-
-#ifndef MOA_PREFILL_POLY
-#define MOA_PREFILL_POLY 1   // of every four column pairs, how many take the polynomial instead of ex2
-#endif
-
 #define MOA_R32(v) \
   v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15], v[16], \
   v[17], v[18], v[19], v[20], v[21], v[22], v[23], v[24], v[25], v[26], v[27], v[28], v[29], v[30], v[31]
@@ -322,14 +248,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
-// 16 consecutive columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -353,32 +271,31 @@ __host__ __device__ constexpr uint32_t make_idesc(int is_bf16, int b_mn_major, i
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// KV chunks (128 tokens = mask blocks 2c and 2c+1) a query super-tile visits, as a list: entries
-// [0, nA) are chunks 0..nA-1 (sink part), entries [nA, nA + nB) are chunks bB, bB+1, ... (band part).
-// A 128-row tile t (query blocks 2t, 2t+1) sees some key of chunk c iff c <= t and
-// (2c < sink_blocks or 2c+1 >= 2t+1-local_blocks), i.e. c < ceil(sink_blocks/2) or c >= t - floor(local_blocks/2).
-struct TileChunks {
+// KV blocks a query super-tile visits, as a list: entries [0, nA) are blocks 0..nA-1 (sink part),
+// entries [nA, nA + nB) are blocks bB, bB+1, ... (band part).
+struct TileBlocks {
   int nA, bB, nB;
   __device__ __forceinline__ int count() const { return nA + nB; }
-  __device__ __forceinline__ int chunk(int u) const { return u < nA ? u : bB + (u - nA); }
+  __device__ __forceinline__ int block(int u) const { return u < nA ? u : bB + (u - nA); }
 };
-// t_lo, t_hi: first and last 128-row tile of the super-tile; nc chunks in the sequence
-__device__ __forceinline__ TileChunks tile_chunks(int t_lo, int t_hi, int nc, int sink_c, int half_l) {
-  const int hi = min(t_hi + 1, nc);                   // chunks [0, hi) are at or below the diagonal
-  TileChunks r;
-  r.nA = max(0, min(sink_c, hi));
-  r.bB = max(r.nA, t_lo - half_l);                    // first band chunk of the first tile
+// t_lo, t_hi: first and last 128-row tile of the super-tile
+__device__ __forceinline__ TileBlocks tile_blocks(int t_lo, int t_hi, int nb, int sink_b, int local_b) {
+  const int hi = min(2 * t_hi + 2, nb);              // blocks [0, hi) are at or below the diagonal
+  TileBlocks r;
+  r.nA = max(0, min(sink_b, hi));
+  r.bB = max(r.nA, 2 * t_lo + 1 - local_b);           // first band block of the first 64 rows
   r.nB = max(0, hi - r.bB);
   return r;
 }
 // The list entries one 128-row tile t takes part in: [0, s_end) and [b_begin, b_end).
+// (Block j is visible to the tile iff j < min(2t+2, nb) and (j < sink or j >= 2t+1-local).)
 struct TileSeen {
   int s_end, b_begin, b_end, total;
   __device__ __forceinline__ int entry(int i) const { return i < s_end ? i : b_begin + (i - s_end); }
 };
-__device__ __forceinline__ TileSeen tile_seen(bool exists, int t, const TileChunks& tb, int nc, int half_l) {
+__device__ __forceinline__ TileSeen tile_seen(bool exists, int t, const TileBlocks& tb, int nb, int local_b) {
   TileSeen r;
-  const int hi = min(t + 1, nc), lo = t - half_l;
+  const int hi = min(2 * t + 2, nb), lo = 2 * t + 1 - local_b;
   r.s_end = exists ? min(tb.nA, hi) : 0;
   r.b_begin = tb.nA + max(lo, tb.bB) - tb.bB;
   r.b_end = tb.nA + min(hi, tb.bB + tb.nB) - tb.bB;
@@ -405,12 +322,11 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int b = blockIdx.z;
   const int h = p.heads_fastest ? blockIdx.x : blockIdx.y;
   const int st = nsuper - 1 - (int)(p.heads_fastest ? blockIdx.y : blockIdx.x);
-  const int nc = (int)((p.N + kBN - 1) / kBN);
+  const int nb = (int)((p.N + kBN - 1) / kBN);
   const int sink_b = p.sink_blocks[h], local_b = p.local_blocks[h];
-  const int sink_c = (sink_b + 1) >> 1, half_l = local_b >> 1;
   const int t0 = 2 * st, t1 = 2 * st + 1;
   const bool active1 = (int64_t)t1 * kBM < p.N;      // the second tile exists
-  const TileChunks tb = tile_chunks(t0, active1 ? t1 : t0, nc, sink_c, half_l);
+  const TileBlocks tb = tile_blocks(t0, active1 ? t1 : t0, nb, sink_b, local_b);
   const int nkv = tb.count();
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr int NH = DH / 64;                 // 64-column panels per tile
@@ -419,23 +335,22 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
-    for (int s = 0; s < kKStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl->k_full[s], 1);
-      mbar_init(&ctl->k_empty[0][s], 1);
-      mbar_init(&ctl->k_empty[1][s], 1);
-    }
-    for (int s = 0; s < kVStages; ++s) {
       mbar_init(&ctl->v_full[s], 1);
-      mbar_init(&ctl->v_empty[0][s], 1);
-      mbar_init(&ctl->v_empty[1][s], 1);
+      for (int x = 0; x < 2; ++x) {
+        mbar_init(&ctl->k_empty[x][s], 1);
+        mbar_init(&ctl->v_empty[x][s], 1);
+      }
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&ctl->s_full[x], 1);
+      mbar_init(&ctl->s_free[x], kSoftmaxThreads);
       mbar_init(&ctl->p_full[x], kSoftmaxThreads);
+      mbar_init(&ctl->pv_done[x], 1);
       mbar_init(&ctl->o_full[x], 1);
     }
     ctl->abort = 0;
-    ctl->pipe_lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) {
@@ -460,30 +375,30 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       int k_issued = 0, v_issued = 0;
       bool ok = true;
-      // V lags K by one chunk: it is needed one MMA step later.  A stage is reused once both
+      // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
       // tiles' issuers have handed it back.
       for (int u = 0; ok && u <= nkv; ++u) {
         if (u < nkv) {
-          const int s = u % kKStages;
-          const uint32_t par = ((u / kKStages) & 1) ^ 1;
+          const int s = u & (kStages - 1);
+          const uint32_t par = ((u / kStages) & 1) ^ 1;
           ok = mbar_wait(&ctl->k_empty[0][s], par, ctl, p.status, kWaitKEmpty) &&
                mbar_wait(&ctl->k_empty[1][s], par, ctl, p.status, kWaitKEmpty);
           if (!ok) break;
           uint8_t* dst = smem + kSmemK + s * kKBytes;
-          const int row = tb.chunk(u) * kBN;
+          const int row = tb.block(u) * kBN;
           mbar_expect_tx(&ctl->k_full[s], NH * kKPanel);
 #pragma unroll
           for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_k, &ctl->k_full[s], 64 * hf, row, h, b);
           k_issued = u + 1;
         }
         if (u >= 1) {
-          const int uv = u - 1, s = uv % kVStages;
-          const uint32_t par = ((uv / kVStages) & 1) ^ 1;
+          const int uv = u - 1, s = uv & (kStages - 1);
+          const uint32_t par = ((uv / kStages) & 1) ^ 1;
           ok = mbar_wait(&ctl->v_empty[0][s], par, ctl, p.status, kWaitVEmpty) &&
                mbar_wait(&ctl->v_empty[1][s], par, ctl, p.status, kWaitVEmpty);
           if (!ok) break;
           uint8_t* dst = smem + kSmemV + s * kKBytes;
-          const int row = tb.chunk(uv) * kBN;
+          const int row = tb.block(uv) * kBN;
           mbar_expect_tx(&ctl->v_full[s], NH * kKPanel);
 #pragma unroll
           for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_v, &ctl->v_full[s], 64 * hf, row, h, b);
@@ -493,13 +408,13 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (*(volatile int*)&ctl->abort) {
         // drain: shared memory must not be released while bulk copies into it are in flight
         const uint64_t tstart = globaltimer_ns();
-        for (int u = max(0, k_issued - kKStages); u < k_issued; ++u) {
-          while (!mbar_try_wait(&ctl->k_full[u % kKStages], (u / kKStages) & 1) &&
+        for (int u = max(0, k_issued - kStages); u < k_issued; ++u) {
+          while (!mbar_try_wait(&ctl->k_full[u & (kStages - 1)], (u / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        for (int u = max(0, v_issued - kVStages); u < v_issued; ++u) {
-          while (!mbar_try_wait(&ctl->v_full[u % kVStages], (u / kVStages) & 1) &&
+        for (int u = max(0, v_issued - kStages); u < v_issued; ++u) {
+          while (!mbar_try_wait(&ctl->v_full[u & (kStages - 1)], (u / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
@@ -509,186 +424,168 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp >= 9) {
     // ------------------------------------------------------------------ MMA issuer of tile x
-    // The whole warp runs this code with warp-uniform control flow and values (so that descriptors and
-    // addresses can live in uniform registers); one elected lane issues the MMAs, commits and arrives.
-    {
+    if (lane == 0) {
       const int x = warp - 9;
-      const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nc, half_l);
+      const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, DH);
       // descriptors differ only in their start-address field (bytes >> 4): build each base once
       const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
-      const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKPanel, 1024);
-      const uint32_t s_tmem = tmem + col_s(x), o_tmem = tmem + col_o(x);
+      const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
+      const uint32_t s_tmem = tmem + col_s(x), o_tmem = tmem + col_o(x), p_tmem = tmem + col_p(x);
       uint64_t* const k_empty = ctl->k_empty[x];
       uint64_t* const v_empty = ctl->v_empty[x];
       bool ok = true;
-      auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
-        const bool mine = mbar_wait(bar, parity, ctl, p.status, code);
-        ok = __all_sync(0xffffffffu, mine);
-      };
+      PROF_DECL
 
       // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).
       // The stage must have been filled first, so that the arrives of successive ring rounds
-      // cannot run ahead of the producer.  K and V are handed back entry by entry, in the order
-      // the producer fills them, which keeps this free of deadlock.
+      // cannot run ahead of the producer.
       auto skip_entries = [&](int from, int to) {
         for (int w = from; ok && w < to; ++w) {
-          const int sk = w % kKStages, sv = w % kVStages;
-          wait(&ctl->k_full[sk], (w / kKStages) & 1, kWaitKFull);
-          if (ok && elect_one()) mbar_arrive(&k_empty[sk]);
-          if (ok) wait(&ctl->v_full[sv], (w / kVStages) & 1, kWaitVFull);
-          if (ok && elect_one()) mbar_arrive(&v_empty[sv]);
+          const int s = w & (kStages - 1);
+          const uint32_t par = (w / kStages) & 1;
+          ok = mbar_wait(&ctl->k_full[s], par, ctl, p.status, kWaitKFull);
+          if (ok) mbar_arrive(&k_empty[s]);
+          if (ok) ok = mbar_wait(&ctl->v_full[s], par, ctl, p.status, kWaitVFull);
+          if (ok) mbar_arrive(&v_empty[s]);
         }
       };
-      // S = Q K^T for list entry u (its K stage is full); the stage goes back to the producer when
-      // these MMAs have read it.  Called by the elected lane.
+      // S = Q K^T for list entry u
       auto issue_qk = [&](int u) {
-        const int s = u % kKStages;
+        const int s = u & (kStages - 1);
+        ok = mbar_wait(&ctl->k_full[s], (u / kStages) & 1, ctl, p.status, kWaitKFull);
+        if (!ok) return;
+        tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-          // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second panel
+          // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
           const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-          tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * kQPanel + off) >> 4),
-                    k_desc + (uint64_t)((half * kKPanel + off) >> 4), idesc_qk, kk > 0);
+          if (!(MOA_PREFILL_DBG & 4))
+          tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
+                    k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
         }
         tc_commit(&ctl->s_full[x]);
-        tc_commit(&k_empty[s]);
-      };
-      // the lock is taken by the elected lane; every lane learns the outcome
-      auto acquire = [&]() {
-        bool got = true;
-        if (elect_one()) got = pipe_acquire(ctl, p.status);
-        ok = __all_sync(0xffffffffu, got);
       };
 
+      // skip_entries interleaves the K and V side entry by entry, which is what keeps it free of
+      // deadlock against a producer that fills K(u) and V(u-1) alternately.
       if (seen.total > 0) {
-        const int u0 = seen.entry(0);
-        skip_entries(0, u0);
-        if (ok) wait(&ctl->q_full, 0, kWaitQ);
-        if (ok) wait(&ctl->k_full[u0 % kKStages], (u0 / kKStages) & 1, kWaitKFull);
-        if (ok) acquire();
-        if (ok) {
-          tc_fence_after();
-          if (elect_one()) {
-            issue_qk(u0);
-            pipe_release(ctl);
-          }
-        }
+        skip_entries(0, seen.entry(0));
+        if (ok) ok = mbar_wait(&ctl->q_full, 0, ctl, p.status, kWaitQ);
+        if (ok) issue_qk(seen.entry(0));
       } else {
         skip_entries(0, nkv);
       }
+      PROF_ADD(0, true);
+      int u_prev = -1;   // entry whose V stage is still to be handed back
       for (int i = 0; ok && i < seen.total; ++i) {
         const int u = seen.entry(i);
-        // The operands that arrive by TMA are waited for first (they are there long before P is), so that
-        // only the turn on the tensor core stands between "P(i) is in TMEM" and the first MMA.
-        const int s = u % kVStages;
-        wait(&ctl->v_full[s], (u / kVStages) & 1, kWaitVFull);
+        const bool has_next = i + 1 < seen.total;
+        const int un = has_next ? seen.entry(i + 1) : u + 1;
+        const bool gap = un != u + 1;   // entries between u and un belong to the other tile only (rare)
+        // (1) the softmax threads hold S(i) in registers: K(u) is done with, the next S may start
+        ok = mbar_wait(&ctl->s_free[x], i & 1, ctl, p.status, kWaitSFree);
         if (!ok) break;
-        const int un = (i + 1 < seen.total) ? seen.entry(i + 1) : -1;
-        const bool gap = un >= 0 && un != u + 1;   // chunks in between belong to the other tile only (rare)
-        if (un >= 0 && !gap) wait(&ctl->k_full[un % kKStages], (un / kKStages) & 1, kWaitKFull);
-        if (!ok) break;
-        // P(i) is in TMEM and O has been rescaled if it had to be
-        wait(&ctl->p_full[x], i & 1, kWaitP);
-        if (!ok) break;
-        if (lane == 0) TRACE_EV(2 + x, i, 0);
-        if (ok) acquire();
-        if (!ok) break;
-        if (lane == 0) TRACE_EV(2 + x, i, 1);
-        tc_fence_after();
-        if (elect_one()) {
-          const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
-#pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live one panel further on
-            tc_mma_ts(o_tmem, s_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
-          }
-          tc_commit(&v_empty[s]);   // the V stage goes back to the producer when these MMAs have read it
-          TRACE_EV(2 + x, i, 2);
-          // issued behind O += P(i) V(i): it overwrites the columns P(i) is read from, in order
-          if (un >= 0 && !gap) issue_qk(un);
-          pipe_release(ctl);
-          TRACE_EV(2 + x, i, 3);
+        PROF_ADD(1, true);
+        mbar_arrive(&k_empty[u & (kStages - 1)]);
+        if (has_next && !gap) {
+          issue_qk(un);
+          if (!ok) break;
         }
-        __syncwarp();
-        if (gap) {
+        PROF_ADD(2, true);
+        // (2) P(i) is in TMEM; the softmax threads waited for P.V(i-1) before writing it, so V(u_prev) is free
+        ok = mbar_wait(&ctl->p_full[x], i & 1, ctl, p.status, kWaitP);
+        if (!ok) break;
+        PROF_ADD(3, true);
+        if (u_prev >= 0) mbar_arrive(&v_empty[u_prev & (kStages - 1)]);
+        const int s = u & (kStages - 1);
+        ok = mbar_wait(&ctl->v_full[s], (u / kStages) & 1, ctl, p.status, kWaitVFull);
+        if (!ok) break;
+        PROF_ADD(4, true);
+        tc_fence_after();
+        const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
+          if (!(MOA_PREFILL_DBG & 4))
+          tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&ctl->pv_done[x]);
+        PROF_ADD(5, true);
+        u_prev = u;
+        if (has_next && gap) {
+          // hand back V(u) through the tensor core's completion, then the other tile's entries, then go on
+          tc_commit(&v_empty[s]);
+          u_prev = -1;
           skip_entries(u + 1, un);
-          if (ok) wait(&ctl->k_full[un % kKStages], (un / kKStages) & 1, kWaitKFull);
-          if (ok) acquire();
-          if (ok) {
-            tc_fence_after();
-            if (elect_one()) {
-              issue_qk(un);
-              pipe_release(ctl);
-            }
-          }
-          __syncwarp();
+          if (ok) issue_qk(un);
         }
       }
       if (ok && seen.total > 0) {
-        if (elect_one()) tc_commit(&ctl->o_full[x]);
-        __syncwarp();
+        tc_commit(&ctl->o_full[x]);
+        if (u_prev >= 0) tc_commit(&v_empty[u_prev & (kStages - 1)]);
         skip_entries(seen.entry(seen.total - 1) + 1, nkv);
       }
+      PROF_FLUSH(16 + 16 * x, true);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = warp >> 2;                              // which query tile this warpgroup owns
     const int tq = t0 + x;
-    const TileSeen seen = tile_seen(x == 0 || active1, tq, tb, nc, half_l);
+    const TileSeen seen = tile_seen(x == 0 || active1, tq, tb, nb, local_b);
     const int row = tid & 127;                            // tile row == TMEM lane
     const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
     const int bi = (int)(i_tok >> 6);
     const int lo_band = bi + 1 - local_b;                 // first band block this row sees
-    const int lo_all = 2 * tq + 2 - local_b;              // band blocks from here on are seen by every row of the tile
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const bool trace_me = (tid & 127) == 0;
-    (void)trace_me;
 
     float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
     float l = 0.f;
     bool ok = true;
+    PROF_DECL
+    const bool prof_me = (tid & 127) == 0;
+    (void)prof_me;
 
     for (int i = 0; i < seen.total; ++i) {
-      const int c = tb.chunk(seen.entry(i));
-      // S(i) complete; the tensor core executes a thread's MMAs in order, so O += P(i-1) V(i-1) is complete too
+      const int jb = tb.block(seen.entry(i));
       ok = mbar_wait(&ctl->s_full[x], i & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (trace_me) TRACE_EV(x, i, 0);
+      PROF_ADD(0, prof_me);
       tc_fence_after();
-      uint32_t sv[kBN];
-#pragma unroll
-      for (int g = 0; g < kBN / 32; ++g) {
-        uint32_t (&part)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * g]);
-        tmem_ld32(lane_base + col_s(x) + 32 * g, part);
+      uint32_t sv[64];
+      {
+        uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+        uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+        if (!(MOA_PREFILL_DBG & 2)) {
+        tmem_ld32(lane_base + col_s(x), lo32);
+        tmem_ld32(lane_base + col_s(x) + 32, hi32);
+        tmem_wait_ld();
+        } else { for (int c = 0; c < 64; ++c) sv[c] = __float_as_uint(0.01f * (float)(c + row)); }
       }
-      tmem_wait_ld();
-      if (trace_me) TRACE_EV(x, i, 1);
-      // a chunk needs an element mask unless both of its blocks are seen in full by every row of the tile
-      const int jb0 = 2 * c;
-      const bool full0 = jb0 < sink_b || jb0 >= lo_all, full1 = jb0 + 1 < sink_b || jb0 + 1 >= lo_all;
-      const bool edge = c >= tq || !(full0 && full1);
+      // S is in registers: let the tensor core start this tile's next S
+      tc_fence_before();
+      mbar_arrive(&ctl->s_free[x]);
+      PROF_ADD(1, prof_me);
+      const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
       if (edge) {
-        const bool sees0 = (jb0 <= bi) && (jb0 < sink_b || jb0 >= lo_band);
-        const bool sees1 = (jb0 + 1 <= bi) && (jb0 + 1 < sink_b || jb0 + 1 >= lo_band);
-        const int64_t j0 = (int64_t)c * kBN;
+        const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
+        const int64_t j0 = (int64_t)jb * kBN;
 #pragma unroll
-        for (int col = 0; col < kBN; ++col) {
-          const bool vis = (col < kBlk ? sees0 : sees1) && (j0 + col <= i_tok) && (j0 + col < p.N);
-          if (!vis) sv[col] = 0xff800000u;  // -inf
+        for (int c = 0; c < 64; ++c) {
+          const bool vis = row_sees && (j0 + c <= i_tok) && (j0 + c < p.N);
+          if (!vis) sv[c] = 0xff800000u;  // -inf
         }
       }
       // row max of the raw scores, four independent chains of three-input max
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int col = 0; col < kBN; col += 8) {
+      for (int c = 0; c < 64; c += 8) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
-          mx[r] = fmax3(mx[r], __uint_as_float(sv[col + 2 * r]), __uint_as_float(sv[col + 2 * r + 1]));
+        for (int r = 0; r < 4; ++r) mx[r] = fmax3(mx[r], __uint_as_float(sv[c + 2 * r]), __uint_as_float(sv[c + 2 * r + 1]));
       }
       // scale_log2 > 0, so the max commutes with the scaling
       const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
@@ -699,36 +596,30 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         m_used = mt;
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      // P row -> TMEM over the first half of the S columns (two values per column, even key in the low half).
-      // Scaling, max subtraction and the row sum run on packed pairs; a fixed share of the pairs takes its
-      // exponential on the FMA pipe, the special-function unit being the scarcer of the two.
-      const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
-      uint64_t ls2[2] = {0ull, 0ull};
+      uint32_t pk[32];
+      // scaling, max subtraction and the row sum on packed pairs (one issue slot for two values)
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+      float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int g = 0; g < kBN / 32; ++g) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int col = 0; col < 32; col += 2) {
-          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[32 * g + col]), __uint_as_float(sv[32 * g + col + 1])), sc2, nm2);
-          float p0, p1;
-          if (((col >> 1) & 3) < MOA_PREFILL_POLY) {
-            exp2_poly2(x2, p0, p1);
-          } else {
-            float x0, x1;
-            f2_unpack(x2, x0, x1);
-            p0 = exp2f(x0);
-            p1 = exp2f(x1);
-          }
-          ls2[(col >> 1) & 1] = f2_add(ls2[(col >> 1) & 1], f2_pack(p0, p1));
-          pk[col >> 1] = Cvt<T>::pack(p0, p1);
-        }
-        tmem_st16(lane_base + col_s(x) + 16 * g, pk);
+      for (int c = 0; c < 64; c += 2) {
+        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, nm2);
+        const float2 p2 = make_float2(exp2f(x2.x), exp2f(x2.y));
+        ls2[(c >> 1) & 1] = __fadd2_rn(ls2[(c >> 1) & 1], p2);
+        pk[c >> 1] = Cvt<T>::pack(p2.x, p2.y);
       }
-      float la, lb, lc, ld;
-      f2_unpack(ls2[0], la, lb);
-      f2_unpack(ls2[1], lc, ld);
-      l = fmaf(l, factor, (la + lb) + (lc + ld));
-      if (trace_me) TRACE_EV(x, i, 2);
+      l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
+      PROF_ADD(2, prof_me);
+      // the tile's previous P.V must be finished before P is overwritten or O rescaled
+      if (i > 0) {
+        ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      PROF_ADD(3, prof_me);
+      // P row -> TMEM (two values per column, even key in the low half)
+      if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_p(x), pk);
+      else if (pk[3] == 0x12345678u) l += 1.f;
       if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 32) {
@@ -736,16 +627,17 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tmem_ld32(lane_base + col_o(x) + c0, ov);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) ov[q] = __float_as_uint(__uint_as_float(ov[q]) * factor);
+          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
           tmem_st32(lane_base + col_o(x) + c0, ov);
         }
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&ctl->p_full[x]);
-      if (trace_me) TRACE_EV(x, i, 3);
+      PROF_ADD(4, prof_me);
     }
 
+    PROF_FLUSH(0, prof_me && x == 0);
     if (ok && seen.total > 0) {
       ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
@@ -764,20 +656,20 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (store) {
           if (OUT_F32) {
 #pragma unroll
-            for (int q = 0; q < 32; q += 4) {
-              float4 f = make_float4(__uint_as_float(ov[q]) * inv_l, __uint_as_float(ov[q + 1]) * inv_l,
-                                     __uint_as_float(ov[q + 2]) * inv_l, __uint_as_float(ov[q + 3]) * inv_l);
-              *reinterpret_cast<float4*>(orow + (c0 + q) * 4) = f;
+            for (int c = 0; c < 32; c += 4) {
+              float4 f = make_float4(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l,
+                                     __uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
+              *reinterpret_cast<float4*>(orow + (c0 + c) * 4) = f;
             }
           } else {
 #pragma unroll
-            for (int q = 0; q < 32; q += 8) {
+            for (int c = 0; c < 32; c += 8) {
               uint4 uo;
-              uo.x = Cvt<T>::pack(__uint_as_float(ov[q]) * inv_l, __uint_as_float(ov[q + 1]) * inv_l);
-              uo.y = Cvt<T>::pack(__uint_as_float(ov[q + 2]) * inv_l, __uint_as_float(ov[q + 3]) * inv_l);
-              uo.z = Cvt<T>::pack(__uint_as_float(ov[q + 4]) * inv_l, __uint_as_float(ov[q + 5]) * inv_l);
-              uo.w = Cvt<T>::pack(__uint_as_float(ov[q + 6]) * inv_l, __uint_as_float(ov[q + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + (c0 + q) * 2) = uo;
+              uo.x = Cvt<T>::pack(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l);
+              uo.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
+              uo.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
+              uo.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = uo;
             }
           }
         }
