@@ -330,13 +330,63 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
     for i in range(warmup):
         step(i)
     ms, _ = time_region(step, steps, device, dist)
+
+    # The step after attention: o_proj (hidden 8192) in its gathered and its row-parallel form, and the
+    # gathered form with the batch split in two so that one half's all-gather runs under the other half's
+    # attention.
+    hidden = Hl * Dl
+    w_full = torch.randn(hidden, Hl * Dl, generator=gen, device=device, dtype=torch.bfloat16) * 0.02
+    w_loc = sh.local_output_columns(w_full, Dl).contiguous()
+
+    def step_gather(i):
+        cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
+        sh.output_projection(out, w_full, mode="gather")
+
+    def step_row(i):
+        cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
+        sh.output_projection(out, w_loc, mode="row_parallel")
+
+    res = {}
+    for name, fn in (("gather", step_gather), ("row_parallel", step_row)):
+        for i in range(warmup):
+            fn(i)
+        t, _ = time_region(fn, steps, device, dist)
+        res[name + "_us"] = t / steps * 1e3
+
+    half = Bl // 2
+    halves = []
+    for part in range(2):
+        c = moa_b200.StaticCircularCache([mine], half, Dl, [[SINK] * len(mine)], device, torch.bfloat16)
+        kk = torch.randn(half, len(mine), fill, Dl, generator=gen, device=device, dtype=torch.bfloat16)
+        c.update(kk, kk, 0)
+        del kk
+        halves.append((c, [t[part * half:(part + 1) * half].contiguous() for t in trio],
+                       torch.empty(half, 1, len(mine), Dl, dtype=torch.bfloat16, device=device)))
+
+    def step_overlap(i):
+        handles = []
+        for part, (c, tr, o) in enumerate(halves):
+            c.decode_attention(tr[0], tr[1], tr[2], 0, sm, out=o)
+            handles.append(sh.all_gather_start(o, slot=part))
+        for h in handles:
+            full = sh.all_gather_finish(h)
+            torch.nn.functional.linear(full.reshape(half, 1, Hl * Dl), w_full)
+
+    for i in range(warmup):
+        step_overlap(i)
+    t, _ = time_region(step_overlap, steps, device, dist)
+    res["gather_two_microbatches_us"] = t / steps * 1e3
+
     kv_bytes_all = moa_b200.decode_bytes(Bl, caps, Dl, 2)
     loads = [sum(caps[h] for h in s) for s in sh.shards]
     return {"workload": "config4 one layer, attention + all-gather: B64 H64 D128 bf16, windows U[1k,16k] + 64 sinks, "
                         f"heads sharded over {world} GPU(s)", "us_per_step": ms / steps * 1e3,
             "tokens_per_s": Bl / (ms / steps * 1e-3), "aggregate_hbm_gbs": kv_bytes_all / (ms / steps * 1e-3) / 1e9,
             "allgather_bytes_per_step": Bl * Hl * Dl * 2 if world > 1 else 0,
-            "shard_imbalance": max(loads) / (sum(loads) / len(loads))}
+            "shard_imbalance": max(loads) / (sum(loads) / len(loads)),
+            "with_o_proj": dict(res, note="attention + o_proj (8192 x 8192 bf16): gathered form, row-parallel form "
+                                          "(all-reduce of partial products), gathered form in two micro-batches "
+                                          "with the all-gather started asynchronously")}
 
 
 def run_gpu(args):

@@ -4,6 +4,14 @@ Heads are independent in attention and each owns its ring cache, so the path sha
 exchange inside attention.  Where a whole layer runs, the per-rank outputs ``(B, q, H/G, D)`` are
 all-gathered into ``(B, q, H, D)`` before ``o_proj`` (NCCL over NVLink; ``gloo`` on CPU in the tests).
 One process per GPU (``torchrun``); nothing here touches peer memory directly.
+
+The step after attention, ``o_proj`` (``MoA/models/llama/modeling_llama.py:329-330`` in the reference),
+comes in two forms here: the gathered one (all-gather the head shards, then the full projection on every
+rank, as the reference's single-GPU code computes it) and a row-parallel one (every rank multiplies its
+heads by its column block of the weight and the partial results are summed with an all-reduce), which
+moves ``1/G`` of the weight per rank instead of all of it.  The all-gather can also be started without
+waiting for it (``all_gather_start`` / ``all_gather_finish``), so that a second micro-batch's attention
+runs while the first one's shards are in flight.
 """
 from __future__ import annotations
 
@@ -67,6 +75,57 @@ class HeadSharding:
             self._gather_buffers[key] = buf
         dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)   # rank r fills rows [r*B, (r+1)*B)
         return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
+
+    def all_gather_start(self, local: Tensor, slot: int = 0):
+        """Starts the all-gather of ``(B, q, H/G, D)`` on the communication stream and returns a handle;
+        work issued before ``all_gather_finish(handle)`` overlaps the transfer.  ``slot`` picks one of
+        several cached buffers, one per gather that is in flight at the same time."""
+        B, q, Hl, D = local.shape
+        if self.world_size == 1:
+            return (None, local, (B, q, Hl, D))
+        key = (local.device, local.dtype, B, q, Hl, D, "async", slot)
+        buf = self._gather_buffers.get(key)
+        if buf is None:
+            buf = torch.empty(self.world_size * B, q, Hl, D, dtype=local.dtype, device=local.device)
+            self._gather_buffers[key] = buf
+        work = dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group, async_op=True)
+        return (work, buf, (B, q, Hl, D))
+
+    def all_gather_finish(self, handle) -> Tensor:
+        """Makes the current stream wait for a gather started with ``all_gather_start`` and returns
+        ``(B, q, H, D)`` in ``order``."""
+        work, buf, (B, q, Hl, D) = handle
+        if work is None:
+            return buf
+        work.wait()
+        return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
+
+    def local_output_columns(self, w_o: Tensor, head_dim: int) -> Tensor:
+        """The column block of an ``o_proj`` weight ``(hidden, H*D)`` (columns already in ``order``, see
+        ``permute_output_projection``) that multiplies this rank's heads."""
+        n = self.heads_per_rank * head_dim
+        return w_o[:, self.rank * n:(self.rank + 1) * n]
+
+    def output_projection(self, local: Tensor, w_o: Tensor, mode: str = "gather") -> Tensor:
+        """``o_proj`` of the sharded attention output ``(B, q, H/G, D)`` -> ``(B, q, hidden)`` on every rank.
+
+        ``mode="gather"``: all-gather the shards and apply the full weight ``w_o (hidden, H*D)`` (columns in
+        ``order``) on every rank.  ``mode="row_parallel"``: ``w_o`` is this rank's column block
+        ``(hidden, H/G*D)`` (``local_output_columns``); partial products are summed over the ranks with an
+        all-reduce, in the tensor's dtype, so the result differs from the gathered form by the rounding of
+        ``G`` partial sums."""
+        B, q, Hl, D = local.shape
+        if mode == "gather":
+            full = self.all_gather(local).reshape(B, q, self.world_size * Hl * D)
+            return torch.nn.functional.linear(full, w_o)
+        if mode != "row_parallel":
+            raise ValueError(f"unknown output projection mode {mode!r}")
+        if w_o.shape[1] != Hl * D:
+            raise ValueError(f"row_parallel expects this rank's column block (hidden, {Hl * D}), got {tuple(w_o.shape)}")
+        part = torch.nn.functional.linear(local.reshape(B, q, Hl * D), w_o)
+        if self.world_size > 1:
+            dist.all_reduce(part, group=self.group)
+        return part
 
     def unpermute(self, gathered: Tensor) -> Tensor:
         """``(B, q, H, D)`` in shard order -> original head order (for checks against an unsharded run)."""

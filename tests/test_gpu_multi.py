@@ -43,8 +43,20 @@ def _worker(rank, world, port, ret):
             ref = full.decode_attention(q, k1, v1, 0, D ** -0.5)
             out = local.decode_attention(q[:, mine].contiguous(), k1[:, mine].contiguous(), v1[:, mine].contiguous(),
                                          0, D ** -0.5)
-            got = sh.unpermute(sh.all_gather(out))
+            gathered = sh.all_gather(out)
+            got = sh.unpermute(gathered)
             worst = max(worst, float((got.float() - ref.float()).abs().max()))
+            # the asynchronous gather returns the same tensor
+            assert torch.equal(sh.all_gather_finish(sh.all_gather_start(out)), gathered)
+            # o_proj: gathered and row-parallel forms against the projection of the single-GPU output
+            w = (torch.randn(256, H * D, generator=gen) * 0.05).half().to(dev)       # columns in head order
+            w_perm = w.view(256, H, D)[:, sh.order].reshape(256, H * D).contiguous()
+            y_ref = torch.nn.functional.linear(ref.reshape(B, 1, H * D).float(), w.float())
+            y_g = sh.output_projection(out, w_perm, mode="gather")
+            y_r = sh.output_projection(out, sh.local_output_columns(w_perm, D).contiguous(), mode="row_parallel")
+            scale = float(y_ref.abs().max())
+            worst = max(worst, float((y_g.float() - y_ref).abs().max()) / scale * 0.25,
+                        float((y_r.float() - y_ref).abs().max()) / scale * 0.25)   # fp16 GEMM: 4e-3 relative
         ret[rank] = worst
     finally:
         dist.destroy_process_group()
