@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Headline workload (BASELINE config 1): one layer of MoA decode with circular KV caches —
+Headline workload (config 1 of BASELINE.json): one layer of MoA decode with circular KV caches —
 batch 16, 32 heads, head_dim 128, fp16, per-head capacity 64 sinks + window W_h drawn from
 {256, 512, 1024, 2048, 4096} (heads sorted by W, as the reference's permute_head arranges),
 caches filled from a 16k-token random sequence, then decode steps with one new token per
@@ -17,7 +17,7 @@ than L2 (126 MB), so no L2 flush is needed between steps.
 With N > 1 (torchrun) every rank owns the ring caches of one 32-head shard (heads, or equally
 layers' caches, sharded; no collective on the data path), so per-GPU work is fixed ("weak").
 
-A second, informational leg times the block-sparse prefill kernel on one layer of BASELINE
+A second, informational leg times the block-sparse prefill kernel on one layer of BASELINE.json
 config 3 (B1 H32 N65536 D128 bf16) and reports dense-equivalent TFLOP/s on the band.
 
 `--impl reference` times the CPU restatement of the reference's own path (ring update +
@@ -257,7 +257,7 @@ def prefill_leg(device, peaks_tf, which, N=65536):
 
 
 def model_leg(device, steps: int = 8, warmup: int = 3, batch: int = 32, context: int = 16384, layers: int = 32):
-    """Informational: BASELINE config 2 — Vicuna-7B-16k architecture (32 layers, hidden 4096, 32 heads x 128,
+    """Informational: config 2 of BASELINE.json — Vicuna-7B-16k architecture (32 layers, hidden 4096, 32 heads x 128,
     FFN 11008, RoPE, fp16) with random-init weights, decode with batch 32 at 16k context on one GPU.
     The per-layer plan is drawn as in config 0 with N = 16384; the ring caches are filled layer by layer
     from random K/V (a 16k-token model prefill at batch 32 is not part of this leg).  One step = one new
@@ -301,7 +301,7 @@ def model_leg(device, steps: int = 8, warmup: int = 3, batch: int = 32, context:
 
 
 def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int = 5):
-    """Informational: the attention part of one decode step of one BASELINE config 4 layer (Llama-3-70B as
+    """Informational: the attention part of one decode step of one layer of config 4 of BASELINE.json (Llama-3-70B as
     MHA: 64 heads x 128, bf16, batch 64, per-head window drawn from U[1k, 16k] rounded to 64, plus 64 sinks,
     rings full).  The 64 heads are placed on the ranks by cost (longest-processing-time packing); every rank
     runs the fused decode launch on its shard and the outputs are all-gathered over NCCL into (B, 1, 64, D).

@@ -24,7 +24,9 @@ import os
 import sys
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
-REF = os.environ.get("MOA_REF", "/root/reference")
+# the reference checkout: MOA_REF, or a directory named "reference" next to this repository
+REF = os.environ.get("MOA_REF") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(
+    os.path.abspath(__file__))))), "reference")
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 

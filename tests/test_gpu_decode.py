@@ -125,7 +125,7 @@ def test_out_may_be_a_slice_of_a_gather_buffer():
 
 
 def test_config1_rings_wrap_and_match_oracle():
-    """BASELINE config 1 at reduced batch: 32 heads, windows from {256..4096} + 64 sinks, caches
+    """Config 1 of BASELINE.json at reduced batch: 32 heads, windows from {256..4096} + 64 sinks, caches
     filled from a 16k-token stream, 256 fused decode steps; every ring crosses its end at step 64."""
     gen = torch.Generator().manual_seed(1001)
     B, H, Dh, N, steps = 2, 32, 128, 16384, 256

@@ -140,7 +140,7 @@ def test_bf16_fp32_store_meets_the_tolerance_and_bf16_store_is_its_rounding():
 
 
 def test_config0_full_size():
-    """BASELINE config 0: B1 H32 N2048 D128 fp16, 64 sinks, span alpha+beta*N per head."""
+    """Config 0 of BASELINE.json: B1 H32 N2048 D128 fp16, 64 sinks, span alpha+beta*N per head."""
     rng = np.random.RandomState(0)
     H, N = 32, 2048
     plan = {"alphas": [[float(rng.choice([128, 256, 512, 1024])) for _ in range(H)]],
