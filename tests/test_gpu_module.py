@@ -186,3 +186,31 @@ def test_real_example_plan_prefill_then_decode():
         a, r = _rel(o1, r1)
         assert a < 2e-3 and r < 1e-3, (step, a, r)
     assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), ocache.cache_update_index[0])
+
+
+def test_flashinfer_compat_calls_like_the_reference_call_sites():
+    """moa_prefill / moa_decode with the arguments of mixture_of_attention.py:436-444 and :466-473."""
+    from moa_b200 import flashinfer_compat as fi
+    g = torch.Generator().manual_seed(11)
+    B, H, N, D = 2, 4, 300, 128
+    q, k, v = (torch.randn(B, H, N, D, generator=g).half() for _ in range(3))
+    sink_size = torch.tensor([64, 64, 128, 64])
+    local_size = torch.tensor([64, 128, 192, 256])
+    out = fi.moa_prefill(q.cuda().transpose(1, 2), k.cuda(), v.cuda(), causal=True,
+                         num_global_blocks=(sink_size // 64).cuda(), num_band_blocks=(local_size // 64).cuda(),
+                         kv_layout="HND")
+    ref = orc.prefill_attention_fp32(q, k, v, D ** -0.5, (sink_size // 64).tolist(), (local_size // 64).tolist())
+    assert out.shape == (B, N, H, D)
+    err = (out.float().cpu() - ref).abs()
+    assert err.max() <= 2e-3 and err.mean() / ref.abs().mean() <= 1e-3
+
+    caps = [128, 192, 320, 128]
+    S = sum(caps)
+    kc, vc = (torch.randn(B, S, D, generator=g).half() for _ in range(2))
+    qd = torch.randn(B, 1, H, D, generator=g).half()
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(caps)[:-1]])).repeat(B, 1)
+    valid = torch.tensor([[128, 100, 320, 7], [1, 192, 64, 128]])
+    got = fi.moa_decode(qd.cuda(), kc.cuda(), vc.cuda(), starts.cuda(), valid.cuda(), D ** -0.5)
+    want = orc.decode_attention_fp32(qd.transpose(1, 2), kc, vc, starts, valid, D ** -0.5)
+    assert got.shape == (B, 1, H, D)
+    assert (got.float().cpu() - want).abs().max() <= 2e-3

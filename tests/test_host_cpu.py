@@ -124,3 +124,13 @@ def test_shard_heads_balances_and_partitions():
         assert max(loads) - min(loads) <= max(caps)
         for s in shards:
             assert [caps[h] for h in s] == sorted(caps[h] for h in s)
+
+
+def test_flashinfer_compat_exports_the_names_the_reference_imports():
+    """MoA/kernels/mixture_of_attention.py:23 imports moa_prefill and moa_decode from its CUDA package."""
+    import inspect
+    from moa_b200 import flashinfer_compat as fi
+    assert list(inspect.signature(fi.moa_prefill).parameters) == [
+        "q", "k", "v", "causal", "num_global_blocks", "num_band_blocks", "kv_layout"]
+    assert list(inspect.signature(fi.moa_decode).parameters) == [
+        "q", "k", "v", "head_start_index", "head_valid_length", "sm_scale"]
