@@ -14,10 +14,16 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 D = 64
 
 
-def _coded(B, H, n, base, dtype, device):
-    """K rows carry (token, head, batch) in dims 0..2 — all exactly representable in fp16/bf16."""
+def _coded(B, H, n, base, dtype, device, split=False):
+    """K rows carry (token, head, batch) in dims 0..2 — all exactly representable in fp16.  With ``split`` the
+    token id is stored as (id % 128, id // 128) in dims 0 and 3, which bf16 (8 significant bits) holds exactly."""
     x = torch.zeros(B, H, n, D, dtype=torch.float32)
-    x[..., 0] = torch.arange(n, dtype=torch.float32)[None, None, :] + base
+    tok = torch.arange(n, dtype=torch.float32)[None, None, :] + base
+    if split:
+        x[..., 0] = tok % 128
+        x[..., 3] = torch.floor(tok / 128)
+    else:
+        x[..., 0] = tok
     x[..., 1] = torch.arange(H, dtype=torch.float32)[None, :, None]
     x[..., 2] = torch.arange(B, dtype=torch.float32)[:, None, None]
     return x.to(dtype).to(device)
@@ -29,7 +35,7 @@ def _decode_golden(g):
     return g % 10000, (g // 10000) % 100, g // 1000000
 
 
-def _check_state(cache, g, step, tag):
+def _check_state(cache, g, step, tag, split=False):
     assert np.array_equal(cache.cache_update_index[0].cpu().numpy(), g["update_index"][step]), (tag, step)
     assert np.array_equal(cache.cache_valid_length[0].cpu().numpy(), g["valid_length"][step]), (tag, step)
     assert np.array_equal(cache.mask_cache[0].cpu().numpy(), g["mask_cache"][step]), (tag, step)
@@ -37,10 +43,15 @@ def _check_state(cache, g, step, tag):
     k = cache.key_cache[0].float().cpu().numpy()
     v = cache.value_cache[0].float().cpu().numpy()
     t, h, b = _decode_golden(g["key0"][step])
-    assert np.array_equal(k[..., 0], t) and np.array_equal(k[..., 1], h) and np.array_equal(k[..., 2], b), (tag, step)
     tv, _, _ = _decode_golden(g["val0"][step])
     frac = g["val0"][step] - np.floor(g["val0"][step])
-    assert np.array_equal(v[..., 0], tv + frac), (tag, step)
+    if split:   # token id in two dims, the V marker (0.5) in dim 4
+        assert np.array_equal(k[..., 0] + 128 * k[..., 3], t), (tag, step)
+        assert np.array_equal(v[..., 0] + 128 * v[..., 3], tv) and np.array_equal(v[..., 4], frac), (tag, step)
+    else:
+        assert np.array_equal(k[..., 0], t), (tag, step)
+        assert np.array_equal(v[..., 0], tv + frac), (tag, step)
+    assert np.array_equal(k[..., 1], h) and np.array_equal(k[..., 2], b), (tag, step)
 
 
 def _mask_of(g, B, n):
@@ -57,23 +68,22 @@ def _mask_of(g, B, n):
 def test_update_replays_reference_trace(path, dtype):
     g = np.load(path)
     B, n = int(g["B"]), int(g["n_prefill"])
-    if dtype == torch.bfloat16 and n + int(g["decode_steps"]) > 127:
-        pytest.skip("token ids + 0.5 above 127.5 are not exact in bf16")
+    split = dtype == torch.bfloat16
     H = len(g["cache_size"][0])
     cache = moa_b200.StaticCircularCache(g["cache_size"].tolist(), B, D, g["static_size"].tolist(), "cuda", dtype)
     base = 0
     for step in range(int(g["decode_steps"]) + 1):
         q = n if step == 0 else 1
-        k = _coded(B, H, q, base, dtype, "cuda")
+        k = _coded(B, H, q, base, dtype, "cuda", split)
         v = k.clone()
-        v[..., 0] += 0.5
+        v[..., 4 if split else 0] += 0.5
         ret = cache.update(k, v, 0, _mask_of(g, B, n) if step == 0 else None)
         base += q
         if step == 0:
             assert ret[0] is k and ret[1] is v          # prefill returns the states it was given
         else:
             assert ret[0] is cache.key_cache[0]         # decode returns the flattened caches
-        _check_state(cache, g, step, os.path.basename(path))
+        _check_state(cache, g, step, os.path.basename(path), split)
 
 
 @pytest.mark.parametrize("name", ["wrap", "short", "leftpad", "exact", "nostatic", "one", "smoke"])
