@@ -475,6 +475,27 @@ def run_gpu(args):
     e2e_drain()
     ms_e2e, win2 = time_region(step_e2e, args.steps, device, dist, drain=e2e_drain)
 
+    # informational: the same K steps captured once in a CUDA graph and replayed (one graph launch per K steps)
+    graph_info = None
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            step_resident(0)
+        main.wait_stream(side)
+        torch.cuda.synchronize(device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(args.steps):
+                step_resident(i)
+        g.replay()
+        torch.cuda.synchronize(device)
+        ms_graph, _ = time_region(lambda i: g.replay() if i == 0 else None, args.steps, device, dist)
+        graph_info = {"us_per_step": ms_graph / args.steps * 1e3,
+                      "note": f"{args.steps} decode steps captured in one CUDA graph, one replay timed"}
+    except Exception as exc:   # capture is an extra, never a reason to lose the bench line
+        graph_info = {"unavailable": repr(exc)[:200]}
+
     hbm_peak, tf_peak, which = measured_peaks()
     prefill = prefill_leg(device, tf_peak, which, args.prefill_n) if (world == 1 and not args.no_prefill) else None
     layer = layer_leg(device, dist, world, rank) if (world > 1 or args.leg == "layer") else None
@@ -507,6 +528,8 @@ def run_gpu(args):
                          "traffic": DECODE_DRAM_TRAFFIC_RATIO * bytes_per_launch},
             "clocks": clocks,
         }
+        if graph_info is not None:
+            line["cuda_graph"] = graph_info
         if prefill is not None:
             line["prefill"] = prefill
         if layer is not None:
