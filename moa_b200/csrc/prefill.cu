@@ -177,6 +177,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Ctl* c
   return mbar_wait_slow(bar, parity, ctl, status, code);
 }
 
+// One lane of a converged warp (the lowest active one).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2, int c3) {
   asm volatile(
@@ -424,7 +435,10 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp >= 9) {
     // ------------------------------------------------------------------ MMA issuer of tile x
-    if (lane == 0) {
+    // The whole warp runs this code with warp-uniform control flow and values, so that descriptors and
+    // addresses can stay in uniform registers; one elected lane issues the MMAs, commits and arrives.
+    // (Issued from lane 0 of a divergent branch the same MMAs cost about three times as many cycles each.)
+    {
       const int x = warp - 9;
       const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
@@ -437,7 +451,10 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       uint64_t* const k_empty = ctl->k_empty[x];
       uint64_t* const v_empty = ctl->v_empty[x];
       bool ok = true;
-      PROF_DECL
+      auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+        const bool mine = mbar_wait(bar, parity, ctl, p.status, code);
+        ok = __all_sync(0xffffffffu, mine);
+      };
 
       // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).
       // The stage must have been filled first, so that the arrives of successive ring rounds
@@ -446,40 +463,41 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int w = from; ok && w < to; ++w) {
           const int s = w & (kStages - 1);
           const uint32_t par = (w / kStages) & 1;
-          ok = mbar_wait(&ctl->k_full[s], par, ctl, p.status, kWaitKFull);
-          if (ok) mbar_arrive(&k_empty[s]);
-          if (ok) ok = mbar_wait(&ctl->v_full[s], par, ctl, p.status, kWaitVFull);
-          if (ok) mbar_arrive(&v_empty[s]);
+          wait(&ctl->k_full[s], par, kWaitKFull);
+          if (ok && elect_one()) mbar_arrive(&k_empty[s]);
+          if (ok) wait(&ctl->v_full[s], par, kWaitVFull);
+          if (ok && elect_one()) mbar_arrive(&v_empty[s]);
         }
       };
       // S = Q K^T for list entry u
       auto issue_qk = [&](int u) {
         const int s = u & (kStages - 1);
-        ok = mbar_wait(&ctl->k_full[s], (u / kStages) & 1, ctl, p.status, kWaitKFull);
+        wait(&ctl->k_full[s], (u / kStages) & 1, kWaitKFull);
         if (!ok) return;
         tc_fence_after();
-        const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
+        if (elect_one()) {
+          const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
-        for (int kk = 0; kk < DH / 16; ++kk) {
-          // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
-          const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-          if (!(MOA_PREFILL_DBG & 4))
-          tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
-                    k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
+          for (int kk = 0; kk < DH / 16; ++kk) {
+            // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
+            const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+            tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
+                      k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
+          }
+          tc_commit(&ctl->s_full[x]);
         }
-        tc_commit(&ctl->s_full[x]);
+        __syncwarp();
       };
 
       // skip_entries interleaves the K and V side entry by entry, which is what keeps it free of
       // deadlock against a producer that fills K(u) and V(u-1) alternately.
       if (seen.total > 0) {
         skip_entries(0, seen.entry(0));
-        if (ok) ok = mbar_wait(&ctl->q_full, 0, ctl, p.status, kWaitQ);
+        if (ok) wait(&ctl->q_full, 0, kWaitQ);
         if (ok) issue_qk(seen.entry(0));
       } else {
         skip_entries(0, nkv);
       }
-      PROF_ADD(0, true);
       int u_prev = -1;   // entry whose V stage is still to be handed back
       for (int i = 0; ok && i < seen.total; ++i) {
         const int u = seen.entry(i);
@@ -487,49 +505,48 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int un = has_next ? seen.entry(i + 1) : u + 1;
         const bool gap = un != u + 1;   // entries between u and un belong to the other tile only (rare)
         // (1) the softmax threads hold S(i) in registers: K(u) is done with, the next S may start
-        ok = mbar_wait(&ctl->s_free[x], i & 1, ctl, p.status, kWaitSFree);
+        wait(&ctl->s_free[x], i & 1, kWaitSFree);
         if (!ok) break;
-        PROF_ADD(1, true);
-        mbar_arrive(&k_empty[u & (kStages - 1)]);
+        if (elect_one()) mbar_arrive(&k_empty[u & (kStages - 1)]);
         if (has_next && !gap) {
           issue_qk(un);
           if (!ok) break;
         }
-        PROF_ADD(2, true);
         // (2) P(i) is in TMEM; the softmax threads waited for P.V(i-1) before writing it, so V(u_prev) is free
-        ok = mbar_wait(&ctl->p_full[x], i & 1, ctl, p.status, kWaitP);
+        wait(&ctl->p_full[x], i & 1, kWaitP);
         if (!ok) break;
-        PROF_ADD(3, true);
-        if (u_prev >= 0) mbar_arrive(&v_empty[u_prev & (kStages - 1)]);
+        if (u_prev >= 0 && elect_one()) mbar_arrive(&v_empty[u_prev & (kStages - 1)]);
         const int s = u & (kStages - 1);
-        ok = mbar_wait(&ctl->v_full[s], (u / kStages) & 1, ctl, p.status, kWaitVFull);
+        wait(&ctl->v_full[s], (u / kStages) & 1, kWaitVFull);
         if (!ok) break;
-        PROF_ADD(4, true);
         tc_fence_after();
-        const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
+        if (elect_one()) {
+          const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
-          if (!(MOA_PREFILL_DBG & 4))
-          tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
+            tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&ctl->pv_done[x]);
+          // a gap: hand back V(u) through the tensor core's completion before the other tile's entries
+          if (has_next && gap) tc_commit(&v_empty[s]);
         }
-        tc_commit(&ctl->pv_done[x]);
-        PROF_ADD(5, true);
+        __syncwarp();
         u_prev = u;
         if (has_next && gap) {
-          // hand back V(u) through the tensor core's completion, then the other tile's entries, then go on
-          tc_commit(&v_empty[s]);
           u_prev = -1;
           skip_entries(u + 1, un);
           if (ok) issue_qk(un);
         }
       }
       if (ok && seen.total > 0) {
-        tc_commit(&ctl->o_full[x]);
-        if (u_prev >= 0) tc_commit(&v_empty[u_prev & (kStages - 1)]);
+        if (elect_one()) {
+          tc_commit(&ctl->o_full[x]);
+          if (u_prev >= 0) tc_commit(&v_empty[u_prev & (kStages - 1)]);
+        }
+        __syncwarp();
         skip_entries(seen.entry(seen.total - 1) + 1, nkv);
       }
-      PROF_FLUSH(16 + 16 * x, true);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
