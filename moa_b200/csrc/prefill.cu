@@ -53,8 +53,7 @@ constexpr int kThreads = 352;
 constexpr uint32_t kTmemCols = 512;
 // TMEM columns: O_A [0,128) O_B [128,256), S_A [256,320) S_B [320,384), P_A [384,416) P_B [416,448)
 __host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
-__host__ __device__ constexpr uint32_t col_s(int x) { return 256u + (uint32_t)x * 64u; }
-__host__ __device__ constexpr uint32_t col_p(int x) { return 384u + (uint32_t)x * 32u; }
+__host__ __device__ constexpr uint32_t col_s(int x, int buf) { return 256u + (uint32_t)x * 128u + (uint32_t)buf * 64u; }
 
 constexpr int kQBytes = kBM * kD * 2;       // 32 KiB per Q tile (two 16 KiB halves: dims 0-63, 64-127)
 constexpr int kKBytes = kBN * kD * 2;       // 16 KiB per K or V tile (two 8 KiB halves)
@@ -79,10 +78,9 @@ struct Ctl {
   uint64_t v_full[kStages];
   uint64_t k_empty[2][kStages];  // [tile]: that tile is done with the K stage
   uint64_t v_empty[2][kStages];
-  uint64_t s_full[2];   // [tile] tensor core -> softmax: S is in TMEM
-  uint64_t s_free[2];   // [tile] softmax -> issuer: S has been read, its columns may be overwritten
+  uint64_t s_full[2][2];   // [tile][S buffer] tensor core -> softmax: S is in TMEM
   uint64_t p_full[2];   // [tile] softmax -> issuer: P is in TMEM (and O rescaled)
-  uint64_t pv_done[2];  // [tile] tensor core -> softmax: O += P V finished (P columns free, O may be touched)
+  uint64_t pv_done[2];  // [tile] tensor core -> softmax: O += P V finished (O may be rescaled)
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
@@ -355,8 +353,8 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
     }
     for (int x = 0; x < 2; ++x) {
-      mbar_init(&ctl->s_full[x], 1);
-      mbar_init(&ctl->s_free[x], kSoftmaxThreads);
+      mbar_init(&ctl->s_full[x][0], 1);
+      mbar_init(&ctl->s_full[x][1], 1);
       mbar_init(&ctl->p_full[x], kSoftmaxThreads);
       mbar_init(&ctl->pv_done[x], 1);
       mbar_init(&ctl->o_full[x], 1);
@@ -438,6 +436,10 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // The whole warp runs this code with warp-uniform control flow and values, so that descriptors and
     // addresses can stay in uniform registers; one elected lane issues the MMAs, commits and arrives.
     // (Issued from lane 0 of a divergent branch the same MMAs cost about three times as many cycles each.)
+    //
+    // Order on the tensor core for this tile: S(0), S(1), then for every step i: O += P(i) V(i), S(i+2).
+    // S(i+2) goes into the buffer P(i) is read from; MMAs of one thread execute in order, so it cannot
+    // overtake that read, and no barrier is needed for the buffer.
     {
       const int x = warp - 9;
       const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
@@ -447,7 +449,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
-      const uint32_t s_tmem = tmem + col_s(x), o_tmem = tmem + col_o(x), p_tmem = tmem + col_p(x);
+      const uint32_t o_tmem = tmem + col_o(x);
       uint64_t* const k_empty = ctl->k_empty[x];
       uint64_t* const v_empty = ctl->v_empty[x];
       bool ok = true;
@@ -456,27 +458,41 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ok = __all_sync(0xffffffffu, mine);
       };
 
-      // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).
-      // The stage must have been filled first, so that the arrives of successive ring rounds
-      // cannot run ahead of the producer.
-      auto skip_entries = [&](int from, int to) {
+      // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).  The stage
+      // must have been filled first, so that the arrives of successive ring rounds cannot run ahead of the
+      // producer.
+      auto skip_k = [&](int from, int to) {
         for (int w = from; ok && w < to; ++w) {
           const int s = w & (kStages - 1);
-          const uint32_t par = (w / kStages) & 1;
-          wait(&ctl->k_full[s], par, kWaitKFull);
+          wait(&ctl->k_full[s], (w / kStages) & 1, kWaitKFull);
           if (ok && elect_one()) mbar_arrive(&k_empty[s]);
-          if (ok) wait(&ctl->v_full[s], par, kWaitVFull);
+        }
+      };
+      auto skip_v = [&](int from, int to) {
+        for (int w = from; ok && w < to; ++w) {
+          const int s = w & (kStages - 1);
+          wait(&ctl->v_full[s], (w / kStages) & 1, kWaitVFull);
           if (ok && elect_one()) mbar_arrive(&v_empty[s]);
         }
       };
-      // S = Q K^T for list entry u
-      auto issue_qk = [&](int u) {
+      // K and V of the same entries, entry by entry in the order the producer fills them
+      auto skip_both = [&](int from, int to) {
+        for (int w = from; ok && w < to; ++w) {
+          skip_k(w, w + 1);
+          skip_v(w, w + 1);
+        }
+      };
+      // S(j) = Q K^T for the tile's j-th entry, into S buffer j & 1; the K stage goes back to the producer
+      // when these MMAs have read it
+      auto issue_qk = [&](int j) {
+        const int u = seen.entry(j);
         const int s = u & (kStages - 1);
         wait(&ctl->k_full[s], (u / kStages) & 1, kWaitKFull);
         if (!ok) return;
         tc_fence_after();
         if (elect_one()) {
           const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
+          const uint32_t s_tmem = tmem + col_s(x, j & 1);
 #pragma unroll
           for (int kk = 0; kk < DH / 16; ++kk) {
             // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
@@ -484,68 +500,57 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
                       k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
           }
-          tc_commit(&ctl->s_full[x]);
+          tc_commit(&ctl->s_full[x][j & 1]);
+          tc_commit(&k_empty[s]);
         }
         __syncwarp();
       };
 
-      // skip_entries interleaves the K and V side entry by entry, which is what keeps it free of
-      // deadlock against a producer that fills K(u) and V(u-1) alternately.
       if (seen.total > 0) {
-        skip_entries(0, seen.entry(0));
+        skip_both(0, seen.entry(0));
         if (ok) wait(&ctl->q_full, 0, kWaitQ);
-        if (ok) issue_qk(seen.entry(0));
+        if (ok) issue_qk(0);
+        if (ok && seen.total > 1) {
+          skip_k(seen.entry(0) + 1, seen.entry(1));
+          if (ok) issue_qk(1);
+        }
       } else {
-        skip_entries(0, nkv);
+        skip_both(0, nkv);
       }
-      int u_prev = -1;   // entry whose V stage is still to be handed back
       for (int i = 0; ok && i < seen.total; ++i) {
         const int u = seen.entry(i);
-        const bool has_next = i + 1 < seen.total;
-        const int un = has_next ? seen.entry(i + 1) : u + 1;
-        const bool gap = un != u + 1;   // entries between u and un belong to the other tile only (rare)
-        // (1) the softmax threads hold S(i) in registers: K(u) is done with, the next S may start
-        wait(&ctl->s_free[x], i & 1, kWaitSFree);
+        // V of entries between the previous step's and this one belongs to the other tile only (rare)
+        if (i > 0) skip_v(seen.entry(i - 1) + 1, u);
         if (!ok) break;
-        if (elect_one()) mbar_arrive(&k_empty[u & (kStages - 1)]);
-        if (has_next && !gap) {
-          issue_qk(un);
-          if (!ok) break;
-        }
-        // (2) P(i) is in TMEM; the softmax threads waited for P.V(i-1) before writing it, so V(u_prev) is free
-        wait(&ctl->p_full[x], i & 1, kWaitP);
-        if (!ok) break;
-        if (u_prev >= 0 && elect_one()) mbar_arrive(&v_empty[u_prev & (kStages - 1)]);
+        // the operand that arrives by TMA is there long before P is: wait for it first
         const int s = u & (kStages - 1);
         wait(&ctl->v_full[s], (u / kStages) & 1, kWaitVFull);
+        if (!ok) break;
+        // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
+        wait(&ctl->p_full[x], i & 1, kWaitP);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
           const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
+          const uint32_t p_tmem = tmem + col_s(x, i & 1);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
             // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
             tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&ctl->pv_done[x]);
-          // a gap: hand back V(u) through the tensor core's completion before the other tile's entries
-          if (has_next && gap) tc_commit(&v_empty[s]);
+          tc_commit(&v_empty[s]);   // the V stage goes back to the producer when these MMAs have read it
         }
         __syncwarp();
-        u_prev = u;
-        if (has_next && gap) {
-          u_prev = -1;
-          skip_entries(u + 1, un);
-          if (ok) issue_qk(un);
+        if (i + 2 < seen.total) {
+          skip_k(seen.entry(i + 1) + 1, seen.entry(i + 2));
+          if (ok) issue_qk(i + 2);
         }
       }
       if (ok && seen.total > 0) {
-        if (elect_one()) {
-          tc_commit(&ctl->o_full[x]);
-          if (u_prev >= 0) tc_commit(&v_empty[u_prev & (kStages - 1)]);
-        }
+        if (elect_one()) tc_commit(&ctl->o_full[x]);
         __syncwarp();
-        skip_entries(seen.entry(seen.total - 1) + 1, nkv);
+        skip_both(seen.entry(seen.total - 1) + 1, nkv);
       }
     }
   } else {
@@ -568,7 +573,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     for (int i = 0; i < seen.total; ++i) {
       const int jb = tb.block(seen.entry(i));
-      ok = mbar_wait(&ctl->s_full[x], i & 1, ctl, p.status, kWaitS);
+      ok = mbar_wait(&ctl->s_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       PROF_ADD(0, prof_me);
@@ -578,14 +583,11 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
         uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
         if (!(MOA_PREFILL_DBG & 2)) {
-        tmem_ld32(lane_base + col_s(x), lo32);
-        tmem_ld32(lane_base + col_s(x) + 32, hi32);
+        tmem_ld32(lane_base + col_s(x, i & 1), lo32);
+        tmem_ld32(lane_base + col_s(x, i & 1) + 32, hi32);
         tmem_wait_ld();
         } else { for (int c = 0; c < 64; ++c) sv[c] = __float_as_uint(0.01f * (float)(c + row)); }
       }
-      // S is in registers: let the tensor core start this tile's next S
-      tc_fence_before();
-      mbar_arrive(&ctl->s_free[x]);
       PROF_ADD(1, prof_me);
       const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
       if (edge) {
@@ -626,18 +628,17 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
       PROF_ADD(2, prof_me);
-      // the tile's previous P.V must be finished before P is overwritten or O rescaled
-      if (i > 0) {
+      PROF_ADD(3, prof_me);
+      // P row -> TMEM, over the first half of the S buffer it came from (two values per column, even key in
+      // the low half).  The buffer's previous reader, P.V(i-2), finished before S(i) was written into it.
+      if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_s(x, i & 1), pk);
+      else if (pk[3] == 0x12345678u) l += 1.f;
+      if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+        // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished
         ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-      }
-      PROF_ADD(3, prof_me);
-      // P row -> TMEM (two values per column, even key in the low half)
-      if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_p(x), pk);
-      else if (pk[3] == 0x12345678u) l += 1.f;
-      if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 32) {
           uint32_t ov[32];
