@@ -3,25 +3,25 @@
 // One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
 // A and B that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
-//              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM and at once hands
-//              the S columns back (so the tensor core can start the tile's next S), computes the
+//              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM, computes the
 //              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
-//              column) to the tile's P columns in TMEM, rescales O in TMEM when the max moved,
-//              and finally runs the epilogue
+//              column) over the first half of the S buffer the row came from, rescales O in TMEM
+//              when the max moved, and finally runs the epilogue
 //   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
 //              two rings of shared-memory stages
-//   warp  9,10 MMA issuers of tile A and tile B (one lane each; warp 9 owns the TMEM allocation):
+//   warp  9,10 MMA issuers of tile A and tile B (warp 9 owns the TMEM allocation):
 //              S = Q K^T (M128 N64 K128, Q and K from shared memory), O += P V (M128 N128 K64,
-//              P from TMEM, V from shared memory as an MN-major operand).  An issuer is a single
-//              thread that competes for issue slots with the softmax warps of its scheduler, so
-//              its loop is kept to a few dozen instructions per step: the KV blocks a tile takes
-//              part in are two index ranges in closed form, and ring stages are handed back with
-//              plain mbarrier arrives wherever completion is already known.
-// Per tile the order is S(i) -> [softmax loads S(i)] -> S(i+1) may start -> [softmax writes P(i)]
-// -> O += P(i) V(i): the next S is computed while the exponentials of the current one run, and
-// the two tiles interleave on the tensor core.  Only the 64-token KV blocks inside "sink U band"
-// of the super-tile are loaded; a tile skips the blocks only the other tile sees, and only the
-// (at most three) edge blocks of a tile get an element mask.
+//              P from TMEM, V from shared memory as an MN-major operand).  The whole warp runs the
+//              issuer loop with warp-uniform control flow (operands stay in uniform registers) and
+//              one elected lane issues; the KV blocks a tile takes part in are two index ranges in
+//              closed form.
+// Each tile has two S/P buffers in TMEM.  On the tensor core its order is S(0), S(1), then per step
+// i: [softmax turns S(i) into P(i)] -> O += P(i) V(i) -> S(i+2), the last one into the buffer P(i)
+// was read from: MMAs of one issuing thread execute in order, so no barrier guards the buffers,
+// and S runs a whole step ahead of the exponentials.  Shared-memory stages go back to the producer
+// through tcgen05.commit.  Only the 64-token KV blocks inside "sink U band" of the super-tile are
+// loaded; a tile skips the blocks only the other tile sees, and only the (at most three) edge
+// blocks of a tile get an element mask.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -51,7 +51,7 @@ constexpr int kStages = 4;         // depth of the K ring and of the V ring (pow
 constexpr int kSoftmaxThreads = 128;  // per tile
 constexpr int kThreads = 352;
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns: O_A [0,128) O_B [128,256), S_A [256,320) S_B [320,384), P_A [384,416) P_B [416,448)
+// TMEM columns: O_A [0,128) O_B [128,256); S/P buffers of tile A [256,320) [320,384), of tile B [384,448) [448,512)
 __host__ __device__ constexpr uint32_t col_o(int x) { return (uint32_t)x * 128u; }
 __host__ __device__ constexpr uint32_t col_s(int x, int buf) { return 256u + (uint32_t)x * 128u + (uint32_t)buf * 64u; }
 
