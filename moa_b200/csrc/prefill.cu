@@ -79,8 +79,10 @@ struct Ctl {
   uint64_t k_empty[2][kStages];  // [tile]: that tile is done with the K stage
   uint64_t v_empty[2][kStages];
   uint64_t s_full[2][2];   // [tile][S buffer] tensor core -> softmax: S is in TMEM
-  uint64_t p_full[2];   // [tile] softmax -> issuer: P is in TMEM (and O rescaled)
-  uint64_t pv_done[2];  // [tile] tensor core -> softmax: O += P V finished (O may be rescaled)
+  uint64_t p_full[2][2];  // [tile][S/P buffer] softmax -> issuer: P is in TMEM (and O rescaled).  One per buffer: the
+                          // softmax threads can be two steps ahead of the issuer, and a single barrier would
+                          // then have advanced two phases, which a parity wait cannot tell from none
+  uint64_t pv_done[2];  // [tile] tensor core -> softmax: the last but one O += P V has finished (O may be rescaled)
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
@@ -355,7 +357,8 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     for (int x = 0; x < 2; ++x) {
       mbar_init(&ctl->s_full[x][0], 1);
       mbar_init(&ctl->s_full[x][1], 1);
-      mbar_init(&ctl->p_full[x], kSoftmaxThreads);
+      mbar_init(&ctl->p_full[x][0], kSoftmaxThreads);
+      mbar_init(&ctl->p_full[x][1], kSoftmaxThreads);
       mbar_init(&ctl->pv_done[x], 1);
       mbar_init(&ctl->o_full[x], 1);
     }
@@ -517,35 +520,60 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       } else {
         skip_both(0, nkv);
       }
+      // Per step: everything that can be checked before P arrives is (V of this step, K of the S two steps
+      // ahead, the other tile's entries in between), so that nothing but the MMAs themselves stands between
+      // "P(i) is in TMEM" and "S(i+2) complete" -- that span has to fit into one softmax step.
+      int u_prev = -1, u = seen.total > 0 ? seen.entry(0) : -1, u1 = seen.total > 1 ? seen.entry(1) : -1;
       for (int i = 0; ok && i < seen.total; ++i) {
-        const int u = seen.entry(i);
-        // V of entries between the previous step's and this one belongs to the other tile only (rare)
-        if (i > 0) skip_v(seen.entry(i - 1) + 1, u);
+        const bool ahead = i + 2 < seen.total;
+        const int u2 = ahead ? seen.entry(i + 2) : -1;
+        // entries between consecutive ones of this tile belong to the other tile only (rare)
+        if (i > 0 && u != u_prev + 1) skip_v(u_prev + 1, u);
+        if (ok && ahead && u2 != u1 + 1) skip_k(u1 + 1, u2);
         if (!ok) break;
-        // the operand that arrives by TMA is there long before P is: wait for it first
-        const int s = u & (kStages - 1);
-        wait(&ctl->v_full[s], (u / kStages) & 1, kWaitVFull);
-        if (!ok) break;
+        const int sv = u & (kStages - 1), sk = u2 & (kStages - 1);
+        {
+          // both TMA operands are normally there already: one poll each, issued back to back
+          const bool v_there = mbar_try_wait(&ctl->v_full[sv], (u / kStages) & 1);
+          const bool k_there = !ahead || mbar_try_wait(&ctl->k_full[sk], (u2 / kStages) & 1);
+          if (!__all_sync(0xffffffffu, v_there && k_there)) {
+            wait(&ctl->v_full[sv], (u / kStages) & 1, kWaitVFull);
+            if (ok && ahead) wait(&ctl->k_full[sk], (u2 / kStages) & 1, kWaitKFull);
+            if (!ok) break;
+          }
+        }
         // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
-        wait(&ctl->p_full[x], i & 1, kWaitP);
+        wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, kWaitP);
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
-          const uint64_t v_desc = v_desc0 + (uint64_t)(s * (kKBytes >> 4));
-          const uint32_t p_tmem = tmem + col_s(x, i & 1);
+          const uint64_t v_desc = v_desc0 + (uint64_t)(sv * (kKBytes >> 4));
+          const uint32_t sp_tmem = tmem + col_s(x, i & 1);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
             // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
-            tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_ts(o_tmem, sp_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
           }
-          tc_commit(&ctl->pv_done[x]);
-          tc_commit(&v_empty[s]);   // the V stage goes back to the producer when these MMAs have read it
+          // "O is quiet" is normally read off the next S (see the softmax side); the last step has no such S
+          if (i + 2 == seen.total) tc_commit(&ctl->pv_done[x]);
+          tc_commit(&v_empty[sv]);   // the V stage goes back to the producer when these MMAs have read it
+          if (ahead) {
+            // S(i+2) into the buffer P(i) is being read from: behind O += P(i) V(i) in this thread's order
+            const uint64_t k_desc = k_desc0 + (uint64_t)(sk * (kKBytes >> 4));
+#pragma unroll
+            for (int kk = 0; kk < DH / 16; ++kk) {
+              const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+              tc_mma_ss(sp_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
+                        k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
+            }
+            tc_commit(&ctl->s_full[x][i & 1]);
+            tc_commit(&k_empty[sk]);
+          }
         }
         __syncwarp();
-        if (i + 2 < seen.total) {
-          skip_k(seen.entry(i + 1) + 1, seen.entry(i + 2));
-          if (ok) issue_qk(i + 2);
-        }
+        u_prev = u;
+        u = u1;
+        u1 = u2;
       }
       if (ok && seen.total > 0) {
         if (elect_one()) tc_commit(&ctl->o_full[x]);
@@ -634,8 +662,12 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_s(x, i & 1), pk);
       else if (pk[3] == 0x12345678u) l += 1.f;
       if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-        // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished
-        ok = mbar_wait(&ctl->pv_done[x], (i - 1) & 1, ctl, p.status, kWaitPV);
+        // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished.  S(i+1)
+        // was issued right behind it by the same thread, so "S(i+1) complete" says so; the last step has no
+        // next S and gets a commit of its own.
+        ok = (i + 1 < seen.total)
+                 ? mbar_wait(&ctl->s_full[x][(i + 1) & 1], ((i + 1) >> 1) & 1, ctl, p.status, kWaitS)
+                 : mbar_wait(&ctl->pv_done[x], 0, ctl, p.status, kWaitPV);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -651,7 +683,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&ctl->p_full[x]);
+      mbar_arrive(&ctl->p_full[x][i & 1]);
       PROF_ADD(4, prof_me);
     }
 
