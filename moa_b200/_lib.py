@@ -5,6 +5,7 @@ wrapper raises ``MoaError`` on a non-zero status.  Build with ``python moa_b200/
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
@@ -94,3 +95,16 @@ def current_stream(device) -> int:
     import torch
 
     return torch.cuda.current_stream(device).cuda_stream
+
+
+_NVTX = os.environ.get("MOA_B200_NVTX") == "1"
+
+
+def nvtx_range(name: str):
+    """NVTX range around a launch when ``MOA_B200_NVTX=1`` (the reference's efficiency script marks its
+    prefill and decode steps the same way, scripts/evaluate/effieicency_test.py:81-83); a no-op otherwise."""
+    if _NVTX:
+        import torch
+
+        return torch.cuda.nvtx.range(name)
+    return contextlib.nullcontext()

@@ -78,7 +78,7 @@ def sparse_prefill(query: Tensor, key: Tensor, value: Tensor, sm_scale: float, s
     assert out.shape == (B, N, H, D) and out.stride(-1) == 1
     assert sink_blocks.dtype == torch.int32 and local_blocks.dtype == torch.int32
     assert sink_blocks.numel() == H and local_blocks.numel() == H
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), _lib.nvtx_range("moa_b200.prefill"):
         _lib.check("moa_prefill_fwd", lib.moa_prefill_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
@@ -107,7 +107,7 @@ def sparse_decode(query: Tensor, key: Tensor, value: Tensor, head_start_index: T
     if out is None:
         out = torch.empty(B, 1, H, D, dtype=query.dtype, device=device)
     ws = _decode_workspace(device, B, H, D, S)
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode"):
         _lib.check("moa_decode_fwd", lib.moa_decode_fwd(
             q.data_ptr(), key.data_ptr(), value.data_ptr(), 0, 0, out.data_ptr(), out.stride(0), out.stride(2),
             hs.data_ptr(), hv.data_ptr(), 0, 0, 0, 0, B, H, D, S, float(sm_scale), _lib.dtype_code(query.dtype),

@@ -201,7 +201,7 @@ class StaticCircularCache:
                         k_new.stride() != v_new.stride():
                     k_new, v_new = k_new.contiguous(), v_new.contiguous()
                 nbs, nhs = k_new.stride(0), k_new.stride(1)
-            with torch.cuda.device(device):
+            with torch.cuda.device(device), _lib.nvtx_range("moa_b200.cache_append"):
                 _lib.check("moa_cache_append", lib.moa_cache_append(
                     kc.data_ptr(), vc.data_ptr(), _lib.ptr(k_new), _lib.ptr(v_new), nbs, nhs,
                     self.cache_head_start_index[layer_idx].data_ptr(), self.cache_valid_length[layer_idx].data_ptr(),
@@ -216,7 +216,7 @@ class StaticCircularCache:
         if k.stride(-1) != 1 or any(s % 8 for s in k.stride()[:-1]) or k.stride() != v.stride():
             k, v = k.contiguous(), v.contiguous()
         pos = count = None
-        with torch.cuda.device(device):
+        with torch.cuda.device(device), _lib.nvtx_range("moa_b200.cache_fill"):
             if attention_mask is not None:
                 assert attention_mask.dim() == 2, \
                     "The shape of the attention mask should be [batch_size, kv_len] and the dtype should be torch.int64."
@@ -273,7 +273,7 @@ class StaticCircularCache:
             cos, sin = rope
             cos, sin = cos.reshape(B, D).contiguous(), sin.reshape(B, D).contiguous()
             assert cos.dtype == self.dtype and sin.dtype == self.dtype and cos.device == device
-            with torch.cuda.device(device):
+            with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode_rope_fused"):
                 _lib.check("moa_decode_rope_fwd", lib.moa_decode_rope_fwd(
                     q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),
                     k_new.data_ptr(), v_new.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), out.stride(0),
@@ -284,7 +284,7 @@ class StaticCircularCache:
                     ws.numel(), self.decode_chunk, _lib.current_stream(device)))
             self._kv_len[layer_idx] += 1
             return out
-        with torch.cuda.device(device):
+        with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode_fused"):
             _lib.check("moa_decode_fwd", lib.moa_decode_fwd(
                 q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),
                 k_new.data_ptr(), v_new.data_ptr(), out.data_ptr(), out.stride(0), out.stride(2),
@@ -308,3 +308,41 @@ class StaticCircularCache:
 
     def reorder_cache(self, beam_idx: torch.LongTensor):
         raise NotImplementedError("Reordering the cache is not implemented currently!")
+
+    # ------------------------------------------------------------------ checkpoint / resume (not in the reference)
+    def state_dict(self) -> Dict[str, Any]:
+        """Everything needed to continue decoding later: the sizes the cache was built with and, per layer,
+        the payload, mask, valid lengths, next write indices and token count.  Tensors are clones."""
+        materialised = [k.device.type != "meta" for k in self.key_cache]
+        return {
+            "cache_size": [list(c) for c in self._cap_host],
+            "static_size": [list(c) for c in self._static_host],
+            "batch_size": self.batch_size,
+            "head_dim": self.head_dim,
+            "dtype": str(self.dtype),
+            "kv_len": list(self._kv_len),
+            "cache_position": self.cache_position,
+            "key_cache": [k.clone() if m else None for k, m in zip(self.key_cache, materialised)],
+            "value_cache": [v.clone() if m else None for v, m in zip(self.value_cache, materialised)],
+            "mask_cache": [t.clone() for t in self.mask_cache],
+            "cache_valid_length": [t.clone() for t in self.cache_valid_length],
+            "cache_update_index": [t.clone() for t in self.cache_update_index],
+        }
+
+    def load_state_dict(self, state: Dict[str, Any]) -> None:
+        """Restores a ``state_dict()`` into a cache built with the same sizes, batch, head_dim and dtype."""
+        if (state["cache_size"] != [list(c) for c in self._cap_host] or
+                state["static_size"] != [list(c) for c in self._static_host] or
+                state["batch_size"] != self.batch_size or state["head_dim"] != self.head_dim or
+                state["dtype"] != str(self.dtype)):
+            raise ValueError("load_state_dict: the state was taken from a cache of a different shape or dtype")
+        for layer in range(self.num_layers):
+            k, v = state["key_cache"][layer], state["value_cache"][layer]
+            if k is not None:     # tensors stay on the device they were saved from; update() moves what it needs
+                self.key_cache[layer] = k.clone()
+                self.value_cache[layer] = v.clone()
+            self.mask_cache[layer] = state["mask_cache"][layer].clone()
+            self.cache_valid_length[layer] = state["cache_valid_length"][layer].clone()
+            self.cache_update_index[layer] = state["cache_update_index"][layer].clone()
+        self._kv_len = list(state["kv_len"])
+        self.cache_position = state["cache_position"]

@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
+from . import _lib
 from .plan import shard_heads
 
 
@@ -57,6 +58,22 @@ class HeadSharding:
         self.heads_per_rank = len(self.local_heads)
         self._gather_buffers: Dict = {}
 
+    def verify_consistent(self) -> None:
+        """Raises on every rank unless all ranks hold the same shard table (built from the same per-head
+        costs): ranks that disagree would gather heads into the wrong places without any other symptom.
+        One small all-gather of the table itself; call it once after construction."""
+        if self.world_size == 1:
+            return
+        mine = torch.tensor(self.order, dtype=torch.int64)
+        if dist.get_backend(self.group) == "nccl":
+            mine = mine.cuda()
+        everyone = [torch.empty_like(mine) for _ in range(self.world_size)]
+        dist.all_gather(everyone, mine, group=self.group)
+        bad = [r for r, t in enumerate(everyone) if not torch.equal(t, everyone[0])]
+        if bad:
+            raise RuntimeError(f"head shard tables differ between ranks (ranks {bad} disagree with rank 0): "
+                               "every rank must build HeadSharding from the same per-head costs")
+
     def slice_plan(self, values: Sequence) -> List:
         """Per-head values (capacities, alphas, ...) of this rank's heads, in shard order."""
         return [values[h] for h in self.local_heads]
@@ -73,7 +90,8 @@ class HeadSharding:
         if buf is None:
             buf = torch.empty(self.world_size * B, q, Hl, D, dtype=local.dtype, device=local.device)
             self._gather_buffers[key] = buf
-        dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)   # rank r fills rows [r*B, (r+1)*B)
+        with _lib.nvtx_range("moa_b200.all_gather"):
+            dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)   # rank r fills rows [r*B, (r+1)*B)
         return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
 
     def all_gather_start(self, local: Tensor, slot: int = 0):

@@ -89,3 +89,67 @@ def test_single_rank_sharding_is_identity():
     assert sh.all_gather(x) is x
     assert sh.order == [1, 2, 0]                       # sorted by cost inside the shard
     assert torch.equal(sh.unpermute(x[:, :, sh.order]), x)
+
+
+# ---------------------------------------------------------------------------------------------------
+# failures, made on the host: ranks that disagree on the shard table; a rank that never joins a gather
+# ---------------------------------------------------------------------------------------------------
+def _mismatch_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        caps = [320, 576, 1088, 320] if rank == 0 else [1088, 576, 320, 320]     # rank 1 read another plan
+        sh = HeadSharding(caps, world, rank)
+        try:
+            sh.verify_consistent()
+            ret[rank] = "no error"
+        except RuntimeError as exc:
+            ret[rank] = str(exc)
+        same = HeadSharding([320, 576, 1088, 320], world, rank)
+        same.verify_consistent()                                                 # agreeing ranks pass
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_with_different_shard_tables_are_detected():
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_mismatch_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        assert len(ret) == world
+        assert all("shard tables differ" in v for v in ret.values()), dict(ret)
+
+
+def _absent_worker(rank, world, port, ret):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    try:
+        sh = HeadSharding([128, 128, 256, 256], world, rank)
+        x = torch.zeros(1, 1, sh.heads_per_rank, 8)
+        sh.all_gather(x)                               # one gather everybody takes part in
+        if rank == 1:
+            ret[rank] = "left between steps"           # leaves with nothing of its own in flight
+            return
+        t0 = time.time()
+        try:
+            sh.all_gather(x)                           # rank 1 never joins this one
+            ret[rank] = "no error"
+        except Exception as exc:                       # the process group's timeout ends the collective
+            ret[rank] = f"error after {time.time() - t0:.1f}s: {type(exc).__name__}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_never_joins_ends_the_gather_with_an_error():
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_absent_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        assert ret[1] == "left between steps"
+        assert ret[0].startswith("error after"), dict(ret)
+        assert float(ret[0].split()[2][:-2]) < 30.0, dict(ret)

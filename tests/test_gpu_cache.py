@@ -165,3 +165,31 @@ def test_random_prefill_then_decode_matches_oracle_bit_exact():
         assert np.array_equal(c.mask_cache[0].cpu().numpy(), o.mask_cache[0])
         assert np.array_equal(c.key_cache[0].cpu().numpy(), o.key_cache[0])
         assert np.array_equal(c.value_cache[0].cpu().numpy(), o.value_cache[0])
+
+
+def test_state_dict_round_trip_continues_bit_exactly():
+    """Checkpoint / resume of the cache: decoding from a restored state gives the same outputs and the same
+    cache as decoding on without interruption."""
+    B, H, Dh, dtype = 2, 3, 64, torch.float16
+    caps, static = [[128, 192, 320]], [[64, 64, 64]]
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    mk = lambda: moa_b200.StaticCircularCache(caps, B, Dh, static, "cuda", dtype)
+    a = mk()
+    k0, v0 = (torch.randn(B, H, 150, Dh, generator=gen, device="cuda").to(dtype) for _ in range(2))
+    a.update(k0, v0, 0)
+    steps = [[torch.randn(B, H, 1, Dh, generator=gen, device="cuda").to(dtype) for _ in range(3)] for _ in range(8)]
+    for q, k, v in steps[:3]:
+        a.decode_attention(q, k, v, 0, 0.125)
+    saved = a.state_dict()
+    outs_a = [a.decode_attention(q, k, v, 0, 0.125).clone() for q, k, v in steps[3:]]
+    b = mk()
+    b.load_state_dict(saved)
+    outs_b = [b.decode_attention(q, k, v, 0, 0.125).clone() for q, k, v in steps[3:]]
+    for x, y in zip(outs_a, outs_b):
+        assert torch.equal(x, y)
+    assert torch.equal(a.key_cache[0], b.key_cache[0]) and torch.equal(a.value_cache[0], b.value_cache[0])
+    assert torch.equal(a.cache_update_index[0], b.cache_update_index[0])
+    assert torch.equal(a.cache_valid_length[0], b.cache_valid_length[0]) and torch.equal(a.mask_cache[0], b.mask_cache[0])
+    assert a._kv_len == b._kv_len
+    with pytest.raises(ValueError):
+        moa_b200.StaticCircularCache([[128, 192, 256]], B, Dh, static, "cuda", dtype).load_state_dict(saved)

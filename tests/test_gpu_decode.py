@@ -217,3 +217,63 @@ def test_rotary_embedding_inside_the_kernel_matches_rotating_first(dtype, Dh):
         assert torch.equal(out_a, out_b), step
     assert torch.equal(a.key_cache[0], b.key_cache[0]) and torch.equal(a.value_cache[0], b.value_cache[0])
     assert torch.equal(a.cache_update_index[0], b.cache_update_index[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_poisoned_unused_slots_and_guard_rows(dtype):
+    """Out-of-range reads and writes, made visible: every cache slot past a head's valid length holds NaN (a
+    kernel that reads one poisons its output), and the output sits between two guard rows that must come
+    back untouched."""
+    gen = torch.Generator().manual_seed(77)
+    B, Dh = 3, 128
+    caps = [128, 192, 320, 64, 1088]
+    H = len(caps)
+    k, v, hs, valid = _random_cache(B, caps, Dh, dtype, gen)
+    q = torch.randn(B, H, 1, Dh, generator=gen).to(dtype)
+    sm = Dh ** -0.5
+    ref = orc.decode_attention_fp32(q, k, v, hs, valid, sm)
+    kp, vp = k.clone(), v.clone()
+    for b in range(B):
+        for h in range(H):
+            lo, hi = int(hs[b, h]) + int(valid[b, h]), int(hs[b, h]) + caps[h]
+            kp[b, lo:hi] = float("nan")
+            vp[b, lo:hi] = float("nan")
+    guard = 1234.5
+    buf = torch.full((B + 2, 1, H, Dh), guard, dtype=dtype, device="cuda")
+    out = moa_b200.sparse_decode(q.cuda(), kp.cuda(), vp.cuda(), hs.cuda(), valid.cuda(), sm, out=buf[1:B + 1])
+    assert torch.isfinite(out.float()).all(), "a slot past the valid length was read"
+    _close(out, ref, dtype, "poisoned cache")
+    assert (buf[0] == guard).all() and (buf[B + 1] == guard).all(), "the output's guard rows were written"
+
+
+def test_fused_decode_leaves_other_slots_alone():
+    """The fused append writes exactly one row per (batch, head): every other slot of caches pre-filled with a
+    marker value, and the guard rows around the flattened caches, keep it."""
+    B, Dh, dtype = 2, 64, torch.float16
+    caps = [128, 192, 320]
+    H = len(caps)
+    cache = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", dtype)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    k0 = torch.randn(B, H, 50, Dh, generator=gen, device="cuda").to(dtype)
+    cache.update(k0, k0, 0)
+    marker = 7.0
+    S = sum(caps)
+    pad = 64
+    # the cache payload lives in the middle of a larger allocation whose first and last rows are guards
+    big_k = torch.full((B * S + 2 * pad, Dh), marker, dtype=dtype, device="cuda")
+    big_v = torch.full((B * S + 2 * pad, Dh), marker, dtype=dtype, device="cuda")
+    written_before = cache.cache_update_index[0].clone()
+    cache.key_cache[0] = big_k[pad:pad + B * S].view(B, S, Dh)
+    cache.value_cache[0] = big_v[pad:pad + B * S].view(B, S, Dh)
+    q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen, device="cuda").to(dtype) for _ in range(3))
+    cache.decode_attention(q, k1, v1, 0, Dh ** -0.5)
+    kc = cache.key_cache[0]
+    touched = torch.zeros(B, S, dtype=torch.bool, device="cuda")
+    touched.scatter_(1, written_before, True)
+    assert (kc[~touched] == marker).all() and (cache.value_cache[0][~touched] == marker).all()
+    for b in range(B):
+        for h in range(H):
+            slot = int(written_before[b, h])
+            assert torch.equal(kc[b, slot], k1[b, h, 0]) and torch.equal(cache.value_cache[0][b, slot], v1[b, h, 0])
+    for big in (big_k, big_v):                                         # nothing outside the cache's own rows
+        assert (big[:pad] == marker).all() and (big[pad + B * S:] == marker).all()

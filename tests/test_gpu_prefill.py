@@ -255,3 +255,29 @@ def test_head_dim_64(dtype):
         _close(out32, ref, "D=64 bf16, fp32 store", 8e-3, 4e-3)
         out16 = _run(q, k, v, sm, sink_b, local_b)
         assert torch.equal(out16.cpu(), out32.cpu().bfloat16())
+
+
+@pytest.mark.parametrize("N", [200, 321, 1000])
+def test_poisoned_rows_past_the_sequence_and_guard_rows(N):
+    """q, k, v are the first N rows of longer buffers whose remaining rows hold NaN (a kernel that reads past
+    the sequence end poisons its output: the TMA boxes of the last tile reach beyond N), and the output is a
+    window of a larger buffer whose rows before and after must keep their marker."""
+    gen = torch.Generator().manual_seed(N)
+    B, H, D, pad = 1, 3, 128, 130
+    sink_b, local_b = [1, 1, 2], [2, 5, 3]
+    big = [torch.randn(B, H, N + pad, D, generator=gen).half() for _ in range(3)]
+    for t in big:
+        t[:, :, N:] = float("nan")
+    q, k, v = (t[:, :, :N] for t in big)
+    ref = orc.prefill_attention_fp32(q, k, v, D ** -0.5, sink_b, local_b)
+    marker = 321.0
+    outbuf = torch.full((B, N + 2 * 64, H, D), marker, dtype=torch.float16, device="cuda")
+    out = outbuf[:, 64:64 + N]
+    qc, kc, vc = (t.cuda()[:, :, :N] for t in big)
+    assert not qc.is_contiguous()
+    moa_b200.sparse_prefill(qc, kc, vc, D ** -0.5, torch.tensor(sink_b, dtype=torch.int32).cuda(),
+                            torch.tensor(local_b, dtype=torch.int32).cuda(), out=out)
+    moa_b200.check_device_status()
+    assert torch.isfinite(out.float()).all(), "rows past the sequence end were read"
+    _close(out, ref, f"poisoned tail, N={N}")
+    assert (outbuf[:, :64] == marker).all() and (outbuf[:, 64 + N:] == marker).all(), "rows outside the output were written"
