@@ -29,11 +29,6 @@
 //
 // Every wait on an mbarrier is bounded: when it runs out the block sets an abort flag, records a
 // code in the status words, drains, frees its TMEM and returns.
-// Development probes (never compiled into the library): MOA_PREFILL_DBG bit 1 skips the softmax
-// threads' TMEM traffic, bit 2 skips the MMAs themselves (barrier handshakes only).
-#ifndef MOA_PREFILL_DBG
-#define MOA_PREFILL_DBG 0
-#endif
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -70,7 +65,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drai
 
 // status codes written to status[0] when a wait gives up
 enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
-       kWaitVFull = 8, kWaitVEmpty = 9, kWaitSFree = 10 };
+       kWaitVFull = 8, kWaitVEmpty = 9 };
 
 struct Ctl {
   uint64_t q_full;
@@ -88,26 +83,6 @@ struct Ctl {
   int abort;
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
-
-#ifdef MOA_PREFILL_PROFILE
-#define PROF_DECL long long _pt = clock64(); long long _pa[16] = {0}; const int _pbase = 0;
-#define PROF_ADD(slot, cond)                     \
-  do {                                           \
-    long long _now = clock64();                  \
-    _pa[(slot) % 16 + 0 * _pbase] += _now - _pt;  \
-    _pt = _now;                                  \
-  } while (0)
-#define PROF_FLUSH(base, cond)                                                                        \
-  do {                                                                                                \
-    if (cond)                                                                                         \
-      for (int _i = 0; _i < 16; ++_i)                                                                 \
-        atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 8 + (base) + _i, (unsigned long long)_pa[_i]); \
-  } while (0)
-#else
-#define PROF_DECL
-#define PROF_ADD(slot, cond)
-#define PROF_FLUSH(base, cond)
-#endif
 
 struct PrefillParams {
   void* out;
@@ -595,28 +570,21 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
     float l = 0.f;
     bool ok = true;
-    PROF_DECL
-    const bool prof_me = (tid & 127) == 0;
-    (void)prof_me;
 
     for (int i = 0; i < seen.total; ++i) {
       const int jb = tb.block(seen.entry(i));
       ok = mbar_wait(&ctl->s_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      PROF_ADD(0, prof_me);
       tc_fence_after();
       uint32_t sv[64];
       {
         uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
         uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
-        if (!(MOA_PREFILL_DBG & 2)) {
         tmem_ld32(lane_base + col_s(x, i & 1), lo32);
         tmem_ld32(lane_base + col_s(x, i & 1) + 32, hi32);
         tmem_wait_ld();
-        } else { for (int c = 0; c < 64; ++c) sv[c] = __float_as_uint(0.01f * (float)(c + row)); }
       }
-      PROF_ADD(1, prof_me);
       const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
       if (edge) {
         const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
@@ -655,12 +623,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         pk[c >> 1] = Cvt<T>::pack(p2.x, p2.y);
       }
       l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
-      PROF_ADD(2, prof_me);
-      PROF_ADD(3, prof_me);
       // P row -> TMEM, over the first half of the S buffer it came from (two values per column, even key in
       // the low half).  The buffer's previous reader, P.V(i-2), finished before S(i) was written into it.
-      if (!(MOA_PREFILL_DBG & 2)) tmem_st32(lane_base + col_s(x, i & 1), pk);
-      else if (pk[3] == 0x12345678u) l += 1.f;
+      tmem_st32(lane_base + col_s(x, i & 1), pk);
       if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
         // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished.  S(i+1)
         // was issued right behind it by the same thread, so "S(i+1) complete" says so; the last step has no
@@ -684,10 +649,8 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&ctl->p_full[x][i & 1]);
-      PROF_ADD(4, prof_me);
     }
 
-    PROF_FLUSH(0, prof_me && x == 0);
     if (ok && seen.total > 0) {
       ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
