@@ -25,6 +25,12 @@ _workspaces: Dict = {}
 _status: Dict = {}
 
 
+# what the waiting thread was waiting for (the codes the prefill kernel writes to its status words)
+_WAIT_NAMES = {1: "Q tiles", 2: "a K tile", 3: "a free K stage", 4: "S from the tensor core", 5: "P from the softmax warps",
+               6: "the last but one P.V", 7: "the final O", 8: "a V tile", 9: "a free V stage",
+               11: "its turn on the tensor core"}
+
+
 def _status_words(device) -> Tensor:
     key = torch.device(device)
     if key not in _status:
@@ -43,8 +49,10 @@ def check_device_status(device=None) -> None:
             words = _status[dev].tolist()
             if words[0] != 0:
                 _status[dev].zero_()
+                what = _WAIT_NAMES.get(words[0], "?")
                 raise _lib.MoaError("moa_prefill_fwd", 5, lib.moa_strerror(5).decode(),
-                                    f"wait code {words[0]} in block x={words[1]} yz={words[2]} thread {words[3]}")
+                                    f"wait code {words[0]} ({what}) in block x={words[1]} yz={words[2]} "
+                                    f"thread {words[3]}")
 
 
 def _decode_workspace(device, B: int, H: int, D: int, S: int) -> Tensor:

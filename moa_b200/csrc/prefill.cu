@@ -65,7 +65,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drai
 
 // status codes written to status[0] when a wait gives up
 enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
-       kWaitVFull = 8, kWaitVEmpty = 9 };
+       kWaitVFull = 8, kWaitVEmpty = 9, kWaitLock = 11 };
 
 struct Ctl {
   uint64_t q_full;
@@ -81,6 +81,7 @@ struct Ctl {
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort;
+  int pipe_lock;   // held by the issuer whose batch of MMAs is being queued
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
 
@@ -162,6 +163,30 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+
+// The two issuers take turns on the tensor core: a tile's batch (O += P V, then the S two steps ahead) is
+// queued as a whole.  Interleaved MMA by MMA, both tiles' S would complete only when all of both batches has
+// run; queued whole, the first tile's S is complete after its own batch, and the tiles drift into opposite
+// phases.  Bounded like every other wait.
+__device__ __forceinline__ bool pipe_acquire(Ctl* ctl, int32_t* status) {
+  const long long t0 = clock64();
+  for (uint32_t spin = 1; atomicCAS(&ctl->pipe_lock, 0, 1) != 0; ++spin) {
+    if ((spin & 255u) == 0) {
+      if (*(volatile int*)&ctl->abort) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *(volatile int*)&ctl->abort = 1;
+        if (atomicCAS(&status[0], 0, kWaitLock) == 0) {
+          status[1] = (int32_t)blockIdx.x;
+          status[2] = (int32_t)(blockIdx.y + 65536 * blockIdx.z);
+          status[3] = (int32_t)threadIdx.x;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void pipe_release(Ctl* ctl) { atomicExch(&ctl->pipe_lock, 0); }
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             int c2, int c3) {
@@ -338,6 +363,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&ctl->o_full[x], 1);
     }
     ctl->abort = 0;
+    ctl->pipe_lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) {
@@ -520,6 +546,12 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
         wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, kWaitP);
         if (!ok) break;
+        {
+          bool got = true;
+          if (elect_one()) got = pipe_acquire(ctl, p.status);
+          ok = __all_sync(0xffffffffu, got);
+          if (!ok) break;
+        }
         tc_fence_after();
         if (elect_one()) {
           const uint64_t v_desc = v_desc0 + (uint64_t)(sv * (kKBytes >> 4));
@@ -544,6 +576,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_commit(&ctl->s_full[x][i & 1]);
             tc_commit(&k_empty[sk]);
           }
+          pipe_release(ctl);
         }
         __syncwarp();
         u_prev = u;
