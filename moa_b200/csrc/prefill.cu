@@ -534,18 +534,19 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (!ok) break;
         const int sv = u & (kStages - 1), sk = u2 & (kStages - 1);
         {
-          // both TMA operands are normally there already: one poll each, issued back to back
+          // The TMA operands are normally there already, and so is P by the time the issuer comes back from
+          // queueing the previous batch: one poll of each barrier, issued back to back, and one vote.
           const bool v_there = mbar_try_wait(&ctl->v_full[sv], (u / kStages) & 1);
           const bool k_there = !ahead || mbar_try_wait(&ctl->k_full[sk], (u2 / kStages) & 1);
-          if (!__all_sync(0xffffffffu, v_there && k_there)) {
+          const bool p_there = mbar_try_wait(&ctl->p_full[x][i & 1], (i >> 1) & 1);
+          if (!__all_sync(0xffffffffu, v_there && k_there && p_there)) {
             wait(&ctl->v_full[sv], (u / kStages) & 1, kWaitVFull);
             if (ok && ahead) wait(&ctl->k_full[sk], (u2 / kStages) & 1, kWaitKFull);
+            // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
+            if (ok) wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, kWaitP);
             if (!ok) break;
           }
         }
-        // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
-        wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, kWaitP);
-        if (!ok) break;
         {
           bool got = true;
           if (elect_one()) got = pipe_acquire(ctl, p.status);
