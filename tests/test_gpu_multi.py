@@ -34,6 +34,7 @@ def _worker(rank, world, port, ret):
         full = moa_b200.StaticCircularCache([caps], B, D, [[64] * H], dev, torch.float16)
         full.update(k, v, 0)
         sh = moa_b200.HeadSharding(caps, world, rank)
+        sh.verify_consistent()                                # every rank built the same shard table
         mine = sh.local_heads
         local = moa_b200.StaticCircularCache([sh.slice_plan(caps)], B, D, [[64] * len(mine)], dev, torch.float16)
         local.update(k[:, mine], v[:, mine], 0)
