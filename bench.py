@@ -239,16 +239,28 @@ def prefill_leg(device, peaks_tf, which, N=65536):
         lb = torch.tensor(local_b, dtype=torch.int32, device=device)
         out = torch.empty(1, N, Hp, D, dtype=torch.bfloat16, device=device)
         sm = D ** -0.5
-        for _ in range(2):
+        for _ in range(3):
             moa_b200.sparse_prefill(q, k, v, sm, sb, lb, out=out)
         moa_b200.check_device_status(device)
-        iters = 3
-        ms, _ = time_region(lambda i: moa_b200.sparse_prefill(q, k, v, sm, sb, lb, out=out), iters, device, None)
+        iters = 5 if N <= 65536 else 3
+        # Timed the way the tensor peak it is compared with was measured (single launches, best of N, CUDA
+        # events on the launching stream); the mean of the same launches back to back is reported beside it.
+        times = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            moa_b200.sparse_prefill(q, k, v, sm, sb, lb, out=out)
+            e1.record()
+            torch.cuda.synchronize(device)
+            times.append(e0.elapsed_time(e1))
         moa_b200.check_device_status(device)
+        ms_best, ms_mean = min(times), sum(times) / len(times)
         flops = moa_b200.prefill_flops(1, N, D, sink_b, local_b)
-        tf = flops / (ms / iters * 1e-3) / 1e12
+        tf = flops / (ms_best * 1e-3) / 1e12
         return {"workload": f"config3 one layer: block-sparse prefill B1 H32 N{N} D128 bf16",
-                "tflops_band_dense_equiv": tf, "ms_per_layer": ms / iters, "flop_per_layer": flops,
+                "tflops_band_dense_equiv": tf, "ms_per_layer": ms_best, "flop_per_layer": flops,
+                "timing": f"best of {iters} single launches (as the peak was measured)",
+                "tflops_mean_of_launches": flops / (ms_mean * 1e-3) / 1e12,
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks_tf, "unit": "TFLOP/s",
                              "frac": tf / peaks_tf, "peak_source": which,
                              "traffic": PREFILL_DRAM_TRAFFIC_RATIO * 4 * Hp * N * D * 2}}

@@ -839,9 +839,10 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
   const int nsuper = (int)((N + 2 * kBM - 1) / (2 * kBM));
-  // fewer super-tiles per head than SMs, and all of K and V fits in L2 with room to spare: interleave the heads
+  // fewer super-tiles per head than SMs, and K and V together not much larger than L2 (126 MB): interleave the
+  // heads.  Measured with 32 heads: +12 % at 8192 tokens (134 MB of K/V), -4 % at 16384 (268 MB).
   const int64_t kv_bytes = (int64_t)B * H * N * D * 2 * 2;
-  p.heads_fastest = (nsuper < 148 && H <= 65535 && kv_bytes <= (64ll << 20)) ? 1 : 0;
+  p.heads_fastest = (nsuper < 148 && H <= 65535 && kv_bytes <= (160ll << 20)) ? 1 : 0;
   dim3 grid = p.heads_fastest ? dim3((unsigned)H, (unsigned)nsuper, (unsigned)B)
                               : dim3((unsigned)nsuper, (unsigned)H, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
