@@ -1,0 +1,159 @@
+"""The prefill kernel's host-checkable arithmetic, restated in Python and checked without a GPU:
+
+* the closed-form lists of KV blocks a 256-row super-tile loads and each of its two 128-row tiles takes part in
+  (``tile_blocks`` / ``tile_seen`` in moa_b200/csrc/prefill.cu) against the block layout of the oracle;
+* the hand-off protocol between the TMA producer and the two MMA issuers over the K and V rings (what each
+  waits for and releases, in the order the kernel does it), simulated with every MMA completing at once:
+  no schedule may end with somebody still waiting.
+"""
+import numpy as np
+import pytest
+
+from oracle import moa_oracle as orc
+
+STAGES = 4
+
+
+def tile_blocks(t_lo, t_hi, nb, sink_b, local_b):
+    hi = min(2 * t_hi + 2, nb)
+    n_a = max(0, min(sink_b, hi))
+    b_b = max(n_a, 2 * t_lo + 1 - local_b)
+    return n_a, b_b, max(0, hi - b_b)
+
+
+def tile_seen(exists, t, tb, nb, local_b):
+    n_a, b_b, n_b = tb
+    hi, lo = min(2 * t + 2, nb), 2 * t + 1 - local_b
+    s_end = min(n_a, hi) if exists else 0
+    b_begin = n_a + max(lo, b_b) - b_b
+    b_end = n_a + min(hi, b_b + n_b) - b_b
+    if not exists or n_b == 0 or b_end < b_begin:
+        b_end = b_begin
+    return [i if i < s_end else b_begin + (i - s_end) for i in range(s_end + b_end - b_begin)]
+
+
+def block_of(tb, u):
+    n_a, b_b, _ = tb
+    return u if u < n_a else b_b + (u - n_a)
+
+
+def lists(n, sink_b, local_b, st):
+    nb = -(-n // 64)
+    t0, t1 = 2 * st, 2 * st + 1
+    active1 = t1 * 128 < n
+    tb = tile_blocks(t0, t1 if active1 else t0, nb, sink_b, local_b)
+    return tb, [tile_seen(True, t0, tb, nb, local_b), tile_seen(active1, t1, tb, nb, local_b)], tb[0] + tb[2]
+
+
+CASES = [(n, s, l) for n in (64, 200, 256, 1000, 2048, 4096, 5000) for s in (0, 1, 2, 3) for l in (1, 2, 3, 7, 16, 40, 100)]
+
+
+@pytest.mark.parametrize("n,sink_b,local_b", CASES)
+def test_tile_lists_are_exactly_the_blocks_the_tile_rows_see(n, sink_b, local_b):
+    nb = -(-n // 64)
+    layout = orc.block_layout(nb, sink_b, local_b)          # [query block, kv block]
+    for st in range(-(-n // 256)):
+        tb, seen, nkv = lists(n, sink_b, local_b, st)
+        loaded = [block_of(tb, u) for u in range(nkv)]
+        assert loaded == sorted(set(loaded)) and all(0 <= b < nb for b in loaded)
+        for x in range(2):
+            qblocks = [qb for qb in (2 * (2 * st + x), 2 * (2 * st + x) + 1) if qb < nb]
+            want = sorted({int(j) for qb in qblocks for j in np.nonzero(layout[qb])[0]})
+            got = [block_of(tb, u) for u in seen[x]]
+            assert got == want, (st, x)
+            assert set(got) <= set(loaded)
+
+
+def simulate(n, sink_b, local_b, st):
+    """Producer and the two issuers as generators that yield what they wait for; returns None when everyone
+    finishes, or the pending waits on a deadlock."""
+    tb, seen, nkv = lists(n, sink_b, local_b, st)
+    kfull, vfull = [0] * STAGES, [0] * STAGES
+    kempty, vempty = [[0] * STAGES for _ in range(2)], [[0] * STAGES for _ in range(2)]
+
+    def producer():
+        for u in range(nkv + 1):
+            if u < nkv:
+                yield ("kempty", u % STAGES, u // STAGES)
+                kfull[u % STAGES] += 1
+            if u >= 1:
+                uv = u - 1
+                yield ("vempty", uv % STAGES, uv // STAGES)
+                vfull[uv % STAGES] += 1
+
+    def issuer(x):
+        sn, total = seen[x], len(seen[x])
+
+        def skip_k(a, b):
+            for w in range(a, b):
+                yield ("kfull", w % STAGES, w // STAGES + 1)
+                kempty[x][w % STAGES] += 1
+
+        def skip_v(a, b):
+            for w in range(a, b):
+                yield ("vfull", w % STAGES, w // STAGES + 1)
+                vempty[x][w % STAGES] += 1
+
+        def skip_both(a, b):
+            for w in range(a, b):
+                yield from skip_k(w, w + 1)
+                yield from skip_v(w, w + 1)
+
+        def qk(j):
+            u = sn[j]
+            yield ("kfull", u % STAGES, u // STAGES + 1)
+            kempty[x][u % STAGES] += 1
+
+        if total == 0:
+            yield from skip_both(0, nkv)
+            return
+        yield from skip_both(0, sn[0])
+        yield from qk(0)
+        if total > 1:
+            yield from skip_k(sn[0] + 1, sn[1])
+            yield from qk(1)
+        u_prev, u, u1 = -1, sn[0], (sn[1] if total > 1 else -1)
+        for i in range(total):
+            ahead = i + 2 < total
+            u2 = sn[i + 2] if ahead else -1
+            if i > 0 and u != u_prev + 1:
+                yield from skip_v(u_prev + 1, u)
+            if ahead and u2 != u1 + 1:
+                yield from skip_k(u1 + 1, u2)
+            yield ("vfull", u % STAGES, u // STAGES + 1)
+            if ahead:
+                yield ("kfull", u2 % STAGES, u2 // STAGES + 1)
+            vempty[x][u % STAGES] += 1          # commit after O += P V
+            if ahead:
+                kempty[x][u2 % STAGES] += 1     # commit after the S two steps ahead
+            u_prev, u, u1 = u, u1, u2
+        yield from skip_both(sn[-1] + 1, nkv)
+
+    def ready(req):
+        kind, s, need = req
+        if kind == "kempty":
+            return kempty[0][s] >= need and kempty[1][s] >= need
+        if kind == "vempty":
+            return vempty[0][s] >= need and vempty[1][s] >= need
+        return (kfull if kind == "kfull" else vfull)[s] >= need
+
+    agents = {"producer": producer(), "issuer A": issuer(0), "issuer B": issuer(1)}
+    pending = {}
+    for name, g in agents.items():
+        pending[name] = next(g, None)
+    while True:
+        progressed = False
+        for name, g in agents.items():
+            while pending[name] is not None and ready(pending[name]):
+                pending[name] = next(g, None)
+                progressed = True
+        if all(v is None for v in pending.values()):
+            return None
+        if not progressed:
+            return dict(pending)
+
+
+@pytest.mark.parametrize("n,sink_b,local_b", CASES)
+def test_ring_protocol_never_deadlocks(n, sink_b, local_b):
+    for st in range(-(-n // 256)):
+        assert simulate(n, sink_b, local_b, st) is None, (st,)
