@@ -157,3 +157,149 @@ def simulate(n, sink_b, local_b, st):
 def test_ring_protocol_never_deadlocks(n, sink_b, local_b):
     for st in range(-(-n // 256)):
         assert simulate(n, sink_b, local_b, st) is None, (st,)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Barrier phases.  An mbarrier wait only sees the parity of the phase it waits for, so a barrier whose
+# signaller can complete phase n+1 before the waiter has looked at phase n reads as "phase n not complete"
+# for ever.  The model below runs producer, issuers and softmax groups under random schedules and checks, at
+# every look at a barrier, that it is at most the awaited phase ahead -- never one more.
+# ---------------------------------------------------------------------------------------------------
+class Barrier:
+    def __init__(self, name):
+        self.name, self.done = name, 0          # number of completed phases
+
+    def look(self, need):
+        """True when phase number ``need`` (1-based) is complete; asserts the parity wait is unambiguous."""
+        assert self.done <= need, f"{self.name}: {self.done} phases complete while phase {need} is awaited"
+        return self.done >= need
+
+
+def simulate_phases(n, sink_b, local_b, st, rng, p_barriers_per_tile):
+    tb, seen, nkv = lists(n, sink_b, local_b, st)
+    kfull = [Barrier(f"k_full[{s}]") for s in range(STAGES)]
+    vfull = [Barrier(f"v_full[{s}]") for s in range(STAGES)]
+    kempty = [[Barrier(f"k_empty[{x}][{s}]") for s in range(STAGES)] for x in range(2)]
+    vempty = [[Barrier(f"v_empty[{x}][{s}]") for s in range(STAGES)] for x in range(2)]
+    sfull = [[Barrier(f"s_full[{x}][{b}]") for b in range(2)] for x in range(2)]
+    pfull = [[Barrier(f"p_full[{x}][{b}]") for b in range(p_barriers_per_tile)] for x in range(2)]
+
+    def p_of(x, i):      # barrier and phase number of "P(i) is ready"
+        return (pfull[x][i & 1], (i >> 1) + 1) if p_barriers_per_tile == 2 else (pfull[x][0], i + 1)
+
+    def producer():
+        for u in range(nkv + 1):
+            if u < nkv:
+                s, need = u % STAGES, u // STAGES
+                while not (kempty[0][s].look(need) and kempty[1][s].look(need)):
+                    yield
+                kfull[s].done += 1
+            if u >= 1:
+                s, need = (u - 1) % STAGES, (u - 1) // STAGES
+                while not (vempty[0][s].look(need) and vempty[1][s].look(need)):
+                    yield
+                vfull[s].done += 1
+
+    def issuer(x):
+        sn, total = seen[x], len(seen[x])
+
+        def wait(bar, need):
+            while not bar.look(need):
+                yield
+
+        def skip(kind, a, b):
+            for w in range(a, b):
+                full, empty = (kfull, kempty) if kind == "k" else (vfull, vempty)
+                yield from wait(full[w % STAGES], w // STAGES + 1)
+                empty[x][w % STAGES].done += 1
+
+        def skip_both(a, b):
+            for w in range(a, b):
+                yield from skip("k", w, w + 1)
+                yield from skip("v", w, w + 1)
+
+        def qk(j):
+            u = sn[j]
+            yield from wait(kfull[u % STAGES], u // STAGES + 1)
+            sfull[x][j & 1].done += 1
+            kempty[x][u % STAGES].done += 1
+
+        if total == 0:
+            yield from skip_both(0, nkv)
+            return
+        yield from skip_both(0, sn[0])
+        yield from qk(0)
+        if total > 1:
+            yield from skip("k", sn[0] + 1, sn[1])
+            yield from qk(1)
+        u_prev, u, u1 = -1, sn[0], (sn[1] if total > 1 else -1)
+        for i in range(total):
+            ahead = i + 2 < total
+            u2 = sn[i + 2] if ahead else -1
+            if i > 0 and u != u_prev + 1:
+                yield from skip("v", u_prev + 1, u)
+            if ahead and u2 != u1 + 1:
+                yield from skip("k", u1 + 1, u2)
+            yield from wait(vfull[u % STAGES], u // STAGES + 1)
+            if ahead:
+                yield from wait(kfull[u2 % STAGES], u2 // STAGES + 1)
+            bar, need = p_of(x, i)
+            yield from wait(bar, need)
+            vempty[x][u % STAGES].done += 1
+            if ahead:
+                sfull[x][i & 1].done += 1
+                kempty[x][u2 % STAGES].done += 1
+            u_prev, u, u1 = u, u1, u2
+        yield from skip_both(sn[-1] + 1, nkv)
+
+    def softmax(x):
+        total = len(seen[x])
+        for i in range(total):
+            while not sfull[x][i & 1].look((i >> 1) + 1):
+                yield
+            if 0 < i < total - 1 and rng.randint(3) == 0:
+                # a rescale of O: "S(i+1) complete" stands for "P.V(i-1) complete"
+                while not sfull[x][(i + 1) & 1].look(((i + 1) >> 1) + 1):
+                    yield
+            p_of(x, i)[0].done += 1
+
+    agents = [producer(), issuer(0), issuer(1), softmax(0), softmax(1)]
+    alive = list(range(len(agents)))
+    idle_rounds = 0
+    while alive:
+        k = alive[rng.randint(len(alive))]
+        before = _snapshot(kfull, vfull, kempty, vempty, sfull, pfull)
+        try:
+            next(agents[k])
+        except StopIteration:
+            alive.remove(k)
+        idle_rounds = idle_rounds + 1 if _snapshot(kfull, vfull, kempty, vempty, sfull, pfull) == before else 0
+        assert idle_rounds < 4000, "nobody makes progress"
+
+
+def _snapshot(*groups):
+    out = []
+    for g in groups:
+        for item in g:
+            out.extend(b.done for b in item) if isinstance(item, list) else out.append(item.done)
+    return out
+
+
+@pytest.mark.parametrize("n,sink_b,local_b", [(4096, 1, 100), (4096, 1, 7), (2048, 2, 3), (1000, 0, 2), (5000, 3, 16)])
+def test_no_barrier_runs_two_phases_ahead_under_random_schedules(n, sink_b, local_b):
+    for seed in range(6):
+        rng = np.random.RandomState(seed)
+        for st in range(0, -(-n // 256), 3):
+            simulate_phases(n, sink_b, local_b, st, rng, p_barriers_per_tile=2)
+
+
+def test_the_model_catches_a_single_p_barrier():
+    """With one "P is ready" barrier per tile the softmax group can complete two phases while the issuer waits
+    for TMA data: the model must notice (this is the stall the kernel once had)."""
+    caught = 0
+    for seed in range(20):
+        try:
+            simulate_phases(4096, 1, 100, 8, np.random.RandomState(seed), p_barriers_per_tile=1)
+        except AssertionError as exc:
+            caught += "p_full" in str(exc)
+    assert caught > 0
