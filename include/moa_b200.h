@@ -164,8 +164,12 @@ int moa_cache_fill(const void* k, const void* v, int64_t sb, int64_t sh, int64_t
  *   out      written as out[b*ob + n*on + h*oh + d]; (B,N,H,D) contiguous is ob=N*H*D, on=H*D, oh=D
  *   sink_blocks, local_blocks (H) int32 device arrays, in 64-token blocks
  *   status   device int32[4], zero on entry; a non-zero word after the kernel finished means a
- *            bounded wait inside the kernel gave up (MOA_ERR_DEVICE_WAIT) and out is invalid
- *   out_f32  non-zero: out is float32 (same math, fp32 store) — used to check the bf16 path
+ *            bounded wait inside the kernel gave up (MOA_ERR_DEVICE_WAIT) and out is invalid.
+ *            status[0] = what was waited for (1 Q tiles, 2 a K tile, 3 a free K stage, 4 S from the
+ *            tensor core, 5 P from the softmax warps, 6 the last but one P.V, 7 the final O, 8 a V
+ *            tile, 9 a free V stage, 11 the issuer's turn on the tensor core); status[1] = blockIdx.x,
+ *            status[2] = blockIdx.y + 65536 * blockIdx.z, status[3] = threadIdx.x of the waiter
+ *   out_f32 non-zero: out is float32 (same math, fp32 store) — used to check the bf16 path
  * ------------------------------------------------------------------------------------------ */
 int moa_prefill_fwd(const void* q, const void* k, const void* v, void* out,
                     int64_t q_sb, int64_t q_sh, int64_t q_sn,
