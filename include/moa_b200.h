@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define MOA_ABI_VERSION 1
+#define MOA_ABI_VERSION 2
 
 typedef void* moa_stream_t; /* a cudaStream_t; NULL is the legacy default stream */
 
@@ -47,11 +47,15 @@ const char* moa_last_error_detail(void);
  * given, also the decode branch of StaticCircularCache.update
  * (MoA/attention/cache_utils.py:1020-1058) in the same launch.
  *
- *   q            (B, H, D)   contiguous; the reference's (B,H,1,D) and (B,1,H,D) are this memory
+ *   q            (B, H, D)   element (b, h, d) at q[b*q_batch_stride + h*q_head_stride + d]: the reference's
+ *                            (B,H,1,D) and (B,1,H,D) are q_batch_stride = H*D, q_head_stride = D; a slice of a
+ *                            fused QKV projection output (B, 3*H*D) is q_batch_stride = 3*H*D.  Rows must be
+ *                            16-byte aligned (pointer aligned, strides multiples of 8 elements)
  *   k_cache,
  *   v_cache      (B, S, D)   contiguous, S = sum of per-head capacities; head h owns rows
  *                            [head_start[b,h], head_start[b,h+1]) (last head: up to S)
- *   k_new, v_new (B, H, D)   both NULL: attention only over the first valid_len[b,h] rows of
+ *   k_new, v_new (B, H, D)   with the element strides (new_batch_stride, new_head_stride), shared by both.
+ *                            Both NULL: attention only over the first valid_len[b,h] rows of
  *                            each head.  Both non-NULL: fused append — the new row is written at
  *                            update_index[b,h], attention runs over the rows that are valid
  *                            after the append (the new token is attended), and afterwards
@@ -59,7 +63,10 @@ const char* moa_last_error_detail(void);
  *                            cache_utils.py:1031-1054 does (kv_len is the layer's _kv_len
  *                            before this step; static_size is static_cache_size[layer]).
  *   out          element (b, h, d) is written at out[b*out_batch_stride + h*out_head_stride + d]
- *                            so (B,1,H,D) and a slice of a wider gather buffer are both possible
+ *                            so (B,1,H,D) and a slice of a wider gather buffer are both possible.
+ *                            A head that owns no rows at all gets zeros.
+ *   out_f32      non-zero: out is float32 (same math, the fp32 result stored unrounded) — the mode the
+ *                            bf16 path is checked in; zero: out has the dtype of q
  *   head_start,
  *   valid_len,
  *   update_index (B, H) int64;  mask_cache (B, S) int64 or NULL;  static_size (H) int64
@@ -72,29 +79,55 @@ const char* moa_last_error_detail(void);
  * ------------------------------------------------------------------------------------------ */
 int64_t moa_decode_workspace_bytes(int B, int H, int D, int64_t S, int chunk);
 int moa_decode_workspace_init(void* workspace, int64_t workspace_bytes, moa_stream_t stream);
-int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
-                   void* out, int64_t out_batch_stride, int64_t out_head_stride,
+int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new, void* out,
+                   int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride,
+                   int64_t new_head_stride, int64_t out_batch_stride, int64_t out_head_stride,
                    const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
                    int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
-                   int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                   int B, int H, int D, int64_t S, float sm_scale, int dtype, int out_f32,
                    void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * moa_decode_rope_fwd: the fused-append decode step with the rotary embedding folded in.
  * Stands for the decode-time sequence of LlamaMixtureAttention.forward
- * (MoA/models/llama/modeling_llama.py:252-326): apply_rotary_pos_emb(q, k) -> cache.update ->
- * attention, in one launch.  q and k_new are the raw projection outputs; rope_cos / rope_sin are
- * this step's (B, D) tables in the tensors' dtype (the position_embeddings the model computes once
- * per forward, Llama rotate_half convention).  The rotated K row is what is stored in the cache.
+ * (MoA/models/llama/modeling_llama.py:234-326): split of the projection output -> apply_rotary_pos_emb(q, k)
+ * -> cache.update -> attention, in one launch.  q and k_new are the raw projection outputs (through their
+ * strides they may be slices of one fused QKV output); rope_cos / rope_sin are this step's (B, D) tables in
+ * the tensors' dtype (the position_embeddings the model computes once per forward, Llama rotate_half
+ * convention).  The rotated K row is what is stored in the cache.
  * Everything else as moa_decode_fwd with k_new/v_new given.
  * ------------------------------------------------------------------------------------------ */
-int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
-                        const void* rope_cos, const void* rope_sin,
-                        void* out, int64_t out_batch_stride, int64_t out_head_stride,
+int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new, void* out,
+                        int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride,
+                        int64_t new_head_stride, int64_t out_batch_stride, int64_t out_head_stride,
                         const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
                         int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
-                        int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                        int B, int H, int D, int64_t S, float sm_scale, int dtype, int out_f32,
+                        const void* rope_cos, const void* rope_sin,
                         void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * moa_decode_gather_fwd: the decode step of a head shard that delivers its output rows to every GPU of
+ * the node in the same launch.  Stands for the attention of LlamaMixtureAttention.forward
+ * (MoA/models/llama/modeling_llama.py:315-326) on one rank plus the gather of the ranks' head shards into
+ * (B, 1, H, D) that has to precede o_proj (:329-330) when heads are sharded; the reference itself is
+ * single-GPU and has no such step.
+ *   out_peers    host array of n_out_peers (0..8) device pointers: the same place (out plus this rank's head
+ *                offset) in the other GPUs' gather buffers, mapped into this process (peer access or symmetric
+ *                memory).  Every output row is stored to out and, with the same strides, to each of them
+ *                (plain stores over NVLink; nothing is loaded from a peer).
+ *   rope_cos/sin both NULL or both given (as moa_decode_rope_fwd).
+ * The launch only writes; the caller must order the peers' reads after it (a barrier across the ranks
+ * after the kernel, before o_proj).  Everything else as moa_decode_fwd.
+ * ------------------------------------------------------------------------------------------ */
+int moa_decode_gather_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                          void* out, int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride,
+                          int64_t new_head_stride, int64_t out_batch_stride, int64_t out_head_stride,
+                          const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
+                          int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
+                          int B, int H, int D, int64_t S, float sm_scale, int dtype, int out_f32,
+                          const void* rope_cos, const void* rope_sin, void* const* out_peers, int n_out_peers,
+                          void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * moa_decode_fwd_static: moa_decode_fwd without the workspace argument.  It has no counterpart
@@ -113,10 +146,11 @@ int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void*
  * ------------------------------------------------------------------------------------------ */
 #define MOA_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
 int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
-                          void* out, int64_t out_batch_stride, int64_t out_head_stride,
+                          void* out, int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride,
+                          int64_t new_head_stride, int64_t out_batch_stride, int64_t out_head_stride,
                           const int64_t* head_start, int64_t* valid_len, int64_t* update_index,
                           int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
-                          int B, int H, int D, int64_t S, float sm_scale, int dtype,
+                          int B, int H, int D, int64_t S, float sm_scale, int dtype, int out_f32,
                           int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

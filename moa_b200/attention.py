@@ -99,10 +99,11 @@ def sparse_prefill(query: Tensor, key: Tensor, value: Tensor, sm_scale: float, s
 
 
 def sparse_decode(query: Tensor, key: Tensor, value: Tensor, head_start_index: Tensor, head_valid_length: Tensor,
-                  sm_scale: float, out: Optional[Tensor] = None) -> Tensor:
+                  sm_scale: float, out: Optional[Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> Tensor:
     """Flash-decoding over the flattened per-head caches (no append).  ``query``: ``(B, H, 1, D)``;
     ``key, value``: ``(B, S, D)`` contiguous; ``head_start_index, head_valid_length``: int64
-    ``(B, H)``.  Returns ``(B, 1, H, D)``."""
+    ``(B, H)``.  Returns ``(B, 1, H, D)``.  ``out_dtype=torch.float32`` stores the fp32 result unrounded
+    (used to check bf16 runs against the oracle at fp16-level tolerance)."""
     B, H, _, D = query.shape
     device = query.device
     assert key.dim() == 3 and value.dim() == 3 and key.shape == value.shape
@@ -110,15 +111,17 @@ def sparse_decode(query: Tensor, key: Tensor, value: Tensor, head_start_index: T
     assert head_start_index.shape == (B, H) and head_valid_length.shape == (B, H)
     assert head_start_index.dtype == torch.int64 and head_valid_length.dtype == torch.int64
     S = key.shape[1]
-    q = query.contiguous()
+    q = query[:, :, 0, :]
+    if not _lib.rows_ok(q):
+        q = q.contiguous()
     hs, hv = head_start_index.contiguous(), head_valid_length.contiguous()
     if out is None:
-        out = torch.empty(B, 1, H, D, dtype=query.dtype, device=device)
+        out = torch.empty(B, 1, H, D, dtype=out_dtype or query.dtype, device=device)
+    assert out.shape == (B, 1, H, D)
     ws = _decode_workspace(device, B, H, D, S)
     with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode"):
         _lib.check("moa_decode_fwd", lib.moa_decode_fwd(
-            q.data_ptr(), key.data_ptr(), value.data_ptr(), 0, 0, out.data_ptr(), out.stride(0), out.stride(2),
-            hs.data_ptr(), hv.data_ptr(), 0, 0, 0, 0, B, H, D, S, float(sm_scale), _lib.dtype_code(query.dtype),
+            *_lib.decode_arguments(q, key, value, None, None, out[:, 0], hs, hv, None, None, None, 0, sm_scale),
             ws.data_ptr(), ws.numel(), 0, _lib.current_stream(device)))
     return out
 

@@ -9,8 +9,9 @@ int64 temporaries, and ``decode_attention`` fuses the append with flash-decoding
 """
 from __future__ import annotations
 
+import ctypes
 import os
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 from torch import Tensor
@@ -242,15 +243,29 @@ class StaticCircularCache:
     # ------------------------------------------------------------------ fused decode step
     def decode_attention(self, query_states: Tensor, key_states: Tensor, value_states: Tensor, layer_idx: int,
                          sm_scale: float, out: Optional[Tensor] = None,
-                         rope: Optional[Tuple[Tensor, Tensor]] = None) -> Tensor:
+                         rope: Optional[Tuple[Tensor, Tensor]] = None, out_dtype: Optional[torch.dtype] = None,
+                         out_peers: Optional[Sequence[int]] = None) -> Tensor:
         """One decode step of one layer in one launch: append the new ``(B, H, 1, D)`` K/V rows at
         the ring's write index, attend over the cache including the new token, advance the
         bookkeeping.  Same result as ``update(...)`` followed by
         ``mixture_of_sparse_attention(...)``.  Returns ``(B, 1, H, D)``; ``out`` may be a
         pre-allocated tensor (or a ``(B, 1, H', D)`` slice of a wider gather buffer).
-        ``rope=(cos, sin)``, tables of shape ``(B, 1, D)`` or ``(B, D)`` in the cache dtype, makes the
-        kernel apply the rotary embedding (Llama ``rotate_half`` convention) to ``query_states`` and
-        ``key_states`` itself; they are then the raw projection outputs."""
+
+        ``query_states, key_states, value_states`` are read through their strides (no copy) as long as
+        their rows are contiguous and 16-byte aligned — e.g. the three slices of one fused QKV
+        projection output.  ``rope=(cos, sin)``, tables of shape ``(B, 1, D)`` or ``(B, D)`` in the cache
+        dtype, makes the kernel apply the rotary embedding (Llama ``rotate_half`` convention) to
+        ``query_states`` and ``key_states`` itself; they are then the raw projection outputs.
+        ``out_dtype=torch.float32`` stores the fp32 result unrounded (parity checks of the bf16 path).
+        ``out_peers``: device addresses of the same slice in other GPUs' gather buffers (mapped into
+        this process); every output row is also stored there, see ``HeadSharding.decode_and_gather``.
+
+        The ring's write rule depends on the layer's token count, which is passed to the kernel by
+        value from the host counter ``_kv_len``: a CUDA graph captured over this call replays the
+        captured count.  That is exact once every ring has left its static part
+        (``_kv_len > max(static_size)``, i.e. after any prompt longer than the sink); the host
+        counters (``_kv_len``, ``cache_position``) are not advanced by a replay — the caller adds the
+        replayed steps itself."""
         H = self.num_head_for_each_layer[layer_idx]
         B, D, S = self.batch_size, self.head_dim, self.layer_cache_size[layer_idx]
         device = query_states.device
@@ -261,38 +276,42 @@ class StaticCircularCache:
         assert query_states.dtype == self.dtype and key_states.dtype == self.dtype and value_states.dtype == self.dtype
         self._materialize(layer_idx, device)
         self._check_layout(layer_idx)
-        q = query_states.contiguous()
-        k_new, v_new = key_states.contiguous(), value_states.contiguous()
+        q = query_states[:, :, 0, :]
+        if not _lib.rows_ok(q):
+            q = q.contiguous()
+        k_new, v_new = key_states[:, :, 0, :], value_states[:, :, 0, :]
+        if not (_lib.rows_ok(k_new) and _lib.rows_ok(v_new) and k_new.stride() == v_new.stride()):
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
         if out is None:
-            out = torch.empty(B, 1, H, D, dtype=self.dtype, device=device)
-        assert out.shape == (B, 1, H, D) and out.stride(-1) == 1 and out.dtype == self.dtype
+            out = torch.empty(B, 1, H, D, dtype=out_dtype or self.dtype, device=device)
+        assert out.shape == (B, 1, H, D) and out.stride(-1) == 1 and out.dtype in (self.dtype, torch.float32)
         ws = self.decode_workspace(layer_idx, device)
         if layer_idx == 0:
             self.cache_position += 1
+        args = _lib.decode_arguments(
+            q, self.key_cache[layer_idx], self.value_cache[layer_idx], k_new, v_new, out[:, 0],
+            self.cache_head_start_index[layer_idx], self.cache_valid_length[layer_idx],
+            self.cache_update_index[layer_idx], self.mask_cache[layer_idx], self.static_cache_size[layer_idx],
+            self._kv_len[layer_idx], sm_scale)
+        tail = (ws.data_ptr(), ws.numel(), self.decode_chunk, _lib.current_stream(device))
+        cos = sin = None
         if rope is not None:
             cos, sin = rope
             cos, sin = cos.reshape(B, D).contiguous(), sin.reshape(B, D).contiguous()
             assert cos.dtype == self.dtype and sin.dtype == self.dtype and cos.device == device
-            with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode_rope_fused"):
-                _lib.check("moa_decode_rope_fwd", lib.moa_decode_rope_fwd(
-                    q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),
-                    k_new.data_ptr(), v_new.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), out.stride(0),
-                    out.stride(2), self.cache_head_start_index[layer_idx].data_ptr(),
-                    self.cache_valid_length[layer_idx].data_ptr(), self.cache_update_index[layer_idx].data_ptr(),
-                    self.mask_cache[layer_idx].data_ptr(), self.static_cache_size[layer_idx].data_ptr(),
-                    self._kv_len[layer_idx], B, H, D, S, float(sm_scale), _lib.dtype_code(self.dtype), ws.data_ptr(),
-                    ws.numel(), self.decode_chunk, _lib.current_stream(device)))
-            self._kv_len[layer_idx] += 1
-            return out
-        with torch.cuda.device(device), _lib.nvtx_range("moa_b200.decode_fused"):
-            _lib.check("moa_decode_fwd", lib.moa_decode_fwd(
-                q.data_ptr(), self.key_cache[layer_idx].data_ptr(), self.value_cache[layer_idx].data_ptr(),
-                k_new.data_ptr(), v_new.data_ptr(), out.data_ptr(), out.stride(0), out.stride(2),
-                self.cache_head_start_index[layer_idx].data_ptr(), self.cache_valid_length[layer_idx].data_ptr(),
-                self.cache_update_index[layer_idx].data_ptr(), self.mask_cache[layer_idx].data_ptr(),
-                self.static_cache_size[layer_idx].data_ptr(), self._kv_len[layer_idx], B, H, D, S, float(sm_scale),
-                _lib.dtype_code(self.dtype), ws.data_ptr(), ws.numel(), self.decode_chunk,
-                _lib.current_stream(device)))
+        with torch.cuda.device(device):
+            if out_peers:
+                peers = (ctypes.c_void_p * len(out_peers))(*[int(a) for a in out_peers])
+                with _lib.nvtx_range("moa_b200.decode_gather"):
+                    _lib.check("moa_decode_gather_fwd", lib.moa_decode_gather_fwd(
+                        *args, _lib.ptr(cos), _lib.ptr(sin), peers, len(out_peers), *tail))
+            elif rope is not None:
+                with _lib.nvtx_range("moa_b200.decode_rope_fused"):
+                    _lib.check("moa_decode_rope_fwd", lib.moa_decode_rope_fwd(
+                        *args, cos.data_ptr(), sin.data_ptr(), *tail))
+            else:
+                with _lib.nvtx_range("moa_b200.decode_fused"):
+                    _lib.check("moa_decode_fwd", lib.moa_decode_fwd(*args, *tail))
         self._kv_len[layer_idx] += 1
         return out
 

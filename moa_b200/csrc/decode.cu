@@ -25,6 +25,7 @@ constexpr int kDecodeThreads = kDecodeWarps * 32;
 #endif
 constexpr int kTileIters = MOA_DECODE_TILE_ITERS;  // 16-byte loads of K (and of V) in flight per thread
 constexpr int kMinChunk = 128, kMaxChunk = 2048;
+constexpr int kMaxOutPeers = 8;
 
 // Rows per block when the caller passes chunk = 0.  A block pays a fixed latency chain (metadata,
 // partial write, ticket) whatever it streams, so chunks should be long; and the grid should fill
@@ -51,6 +52,10 @@ struct DecodeParams {
   const void* v_new;
   void* out;
   int64_t out_bs, out_hs;
+  void* out_peer[kMaxOutPeers];  // further destinations of every output row (other GPUs' gather buffers)
+  int n_out_peers;
+  int64_t q_bs, q_hs;      // element strides of q (a row of D contiguous)
+  int64_t new_bs, new_hs;  // element strides shared by k_new and v_new
   const int64_t* head_start;
   int64_t* valid_len;
   int64_t* update_index;
@@ -104,7 +109,24 @@ __device__ __forceinline__ uint4 rope8(const uint4& x, const T* cos_row, const T
   return o;
 }
 
-template <typename T, int D>
+// Element d of output row (b, h): to `out` and to every further destination (same strides).  OUT_F32 stores
+// the fp32 value (the mode the bf16 path is checked in); otherwise it is rounded once to T.
+template <typename T, bool OUT_F32>
+__device__ __forceinline__ void store_out(const DecodeParams& p, int b, int h, int d, float o) {
+  const int64_t off = (int64_t)b * p.out_bs + (int64_t)h * p.out_hs + d;
+  if (OUT_F32) {
+    reinterpret_cast<float*>(p.out)[off] = o;
+#pragma unroll 1
+    for (int g = 0; g < p.n_out_peers; ++g) reinterpret_cast<float*>(p.out_peer[g])[off] = o;
+  } else {
+    const T v = static_cast<T>(o);
+    reinterpret_cast<T*>(p.out)[off] = v;
+#pragma unroll 1
+    for (int g = 0; g < p.n_out_peers; ++g) reinterpret_cast<T*>(p.out_peer[g])[off] = v;
+  }
+}
+
+template <typename T, int D, bool OUT_F32>
 __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const DecodeParams p) {
   constexpr int LPR = D / 8;    // lanes that share one cache row (16 bytes each)
   constexpr int RPI = 32 / LPR; // rows a warp covers with one load instruction
@@ -130,6 +152,16 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
   const T* kc = reinterpret_cast<const T*>(p.k_cache) + (int64_t)b * p.S * D;
   const T* vc = reinterpret_cast<const T*>(p.v_cache) + (int64_t)b * p.S * D;
 
+  // Heads without any rows (head_start[h] == head_start[h+1]) are nobody's chunk: the first block of the
+  // batch row writes their (all-zero) output, so that every (b, h) row of `out` is defined.
+  if (c == 0) {
+    for (int h = 0; h < p.H; ++h) {
+      const int64_t hs = hs_row[h];
+      const int64_t he = (h + 1 < p.H) ? hs_row[h + 1] : p.S;
+      if (he <= hs && tid < D) store_out<T, OUT_F32>(p, b, h, tid, 0.f);
+    }
+  }
+
   for (int h = find_head(hs_row, p.H, lo, lane); h < p.H; ++h) {
     const int64_t hs = hs_row[h];
     if (hs >= hi) break;
@@ -142,8 +174,9 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
     const int64_t valid_post = fused ? valid_pre + (valid_pre < cap ? 1 : 0) : valid_pre;
     const int64_t seg_lo = max(lo, hs);
     const int64_t seg_hi = min(hi, hs + valid_post);
-    const T* knew = fused ? reinterpret_cast<const T*>(p.k_new) + bh * D : nullptr;
-    const T* vnew = fused ? reinterpret_cast<const T*>(p.v_new) + bh * D : nullptr;
+    const int64_t new_off = (int64_t)b * p.new_bs + (int64_t)h * p.new_hs;
+    const T* knew = fused ? reinterpret_cast<const T*>(p.k_new) + new_off : nullptr;
+    const T* vnew = fused ? reinterpret_cast<const T*>(p.v_new) + new_off : nullptr;
 
     // Fused append: the block whose chunk holds the write slot stores the new K and V rows (K with the
     // rotary embedding applied when cos/sin are given), then the whole block reads them back from the
@@ -169,7 +202,8 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
     // q slice of this lane (rotated if asked), pre-scaled so that softmax runs in base 2
     float qf[8];
     {
-      uint4 qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + bh * D + li * 8);
+      uint4 qu = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_bs +
+                                                 (int64_t)h * p.q_hs + li * 8);
       if (rope) qu = rope8<T, LPR>(qu, cos_row, sin_row, li, 0xffffffffull);
       unpack8<T>(qu, qf);
 #pragma unroll
@@ -287,10 +321,7 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
       }
     }
     if (last) {
-      if (tid < D) {
-        const float o = (L > 0.f) ? O / L : 0.f;
-        reinterpret_cast<T*>(p.out)[(int64_t)b * p.out_bs + (int64_t)h * p.out_hs + tid] = static_cast<T>(o);
-      }
+      if (tid < D) store_out<T, OUT_F32>(p, b, h, tid, (L > 0.f) ? O / L : 0.f);
       if (fused && tid == 0) {
         // every other block of this head has already read the old values (it took its ticket
         // after reading them), so the metadata can advance now
@@ -303,30 +334,36 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
   }
 }
 
-// Resident-block slots of the current device for this kernel; 148 x 5 if no device can be asked
-// (a build or test machine without a GPU).
+// Resident-block slots of the current device for this kernel (kept per device ordinal: one process may
+// drive several GPUs); 148 x 5 if no device can be asked (a build or test machine without a GPU).
+constexpr int kMaxDevices = 64;
 int decode_slots() {
-  static int cached = 0;
-  if (cached > 0) return cached;
+  static int cached[kMaxDevices];   // zero-initialised; benign race: every writer stores the same value
   int dev = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess &&
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moa_decode_kernel<__half, 128>, kDecodeThreads, 0) ==
-          cudaSuccess &&
-      sms > 0 && per_sm > 0) {
-    cached = sms * per_sm;
-  } else {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
     (void)cudaGetLastError();
     return 148 * 5;
   }
-  return cached;
+  if (cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moa_decode_kernel<__half, 128, false>, kDecodeThreads,
+                                                    0) == cudaSuccess &&
+      sms > 0 && per_sm > 0) {
+    cached[dev] = sms * per_sm;
+    return cached[dev];
+  }
+  (void)cudaGetLastError();
+  return 148 * 5;
 }
 
 template <typename T>
-int launch_decode(const DecodeParams& p, int D, dim3 grid, cudaStream_t stream) {
-  switch (D) {
-    case 64: moa_decode_kernel<T, 64><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-    case 128: moa_decode_kernel<T, 128><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+int launch_decode(const DecodeParams& p, int D, bool out_f32, dim3 grid, cudaStream_t stream) {
+  const int variant = (D == 64 ? 0 : D == 128 ? 2 : -1);
+  switch (variant < 0 ? -1 : variant + (out_f32 ? 1 : 0)) {
+    case 0: moa_decode_kernel<T, 64, false><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+    case 1: moa_decode_kernel<T, 64, true><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+    case 2: moa_decode_kernel<T, 128, false><<<grid, kDecodeThreads, 0, stream>>>(p); break;
+    case 3: moa_decode_kernel<T, 128, true><<<grid, kDecodeThreads, 0, stream>>>(p); break;
     default: set_error_text("decode: head_dim must be 64 or 128"); return MOA_ERR_UNSUPPORTED;
   }
   MOA_CUDA_CHECK(cudaGetLastError());
@@ -345,45 +382,93 @@ inline WsLayout ws_layout(int B, int H, int D, int64_t S, int chunk) {
   return w;
 }
 
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 }  // namespace
 
+// What every decode entry point passes on (the C ABI spells these out as plain arguments).
+struct DecodeCall {
+  const void* q; void* k_cache; void* v_cache; const void* k_new; const void* v_new; void* out;
+  int64_t q_bs, q_hs, new_bs, new_hs, out_bs, out_hs;
+  const int64_t* head_start; int64_t* valid_len; int64_t* update_index; int64_t* mask_cache;
+  const int64_t* static_size; int64_t kv_len;
+  int B, H, D; int64_t S; float sm_scale; int dtype, out_f32;
+  void* workspace; int64_t workspace_bytes; int chunk; cudaStream_t stream;
+  const void* rope_cos; const void* rope_sin;
+  void* const* out_peers; int n_out_peers;
+};
+
 // Validates the arguments, lays out the workspace and launches the kernel.
-int decode_launch_with_scratch(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
-                               void* out, int64_t out_bs, int64_t out_hs, const int64_t* head_start,
-                               int64_t* valid_len, int64_t* update_index, int64_t* mask_cache,
-                               const int64_t* static_size, int64_t kv_len, int B, int H, int D, int64_t S,
-                               float sm_scale, int dtype, void* workspace, int64_t workspace_bytes, int chunk,
-                               cudaStream_t stream, const void* rope_cos = nullptr, const void* rope_sin = nullptr) {
-  MOA_REQUIRE(q && k_cache && v_cache && out && head_start && valid_len, "decode: null pointer");
-  MOA_REQUIRE((k_new == nullptr) == (v_new == nullptr), "decode: k_new and v_new must both be given or both be NULL");
-  MOA_REQUIRE(B > 0 && H > 0 && S > 0 && B <= 65535, "decode: bad shape");
-  if (k_new) MOA_REQUIRE(update_index && static_size, "decode: fused append needs update_index and static_size");
-  MOA_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "decode: rope_cos and rope_sin go together");
-  MOA_REQUIRE(rope_cos == nullptr || k_new != nullptr, "decode: the rotary embedding is applied in the fused-append mode only");
-  if (chunk <= 0) chunk = auto_chunk(B, S);
-  const WsLayout w = ws_layout(B, H, D, S, chunk);
-  if (!workspace || workspace_bytes < w.total) {
+int decode_launch_with_scratch(const DecodeCall& a) {
+  MOA_REQUIRE(a.q && a.k_cache && a.v_cache && a.out && a.head_start && a.valid_len, "decode: null pointer");
+  MOA_REQUIRE((a.k_new == nullptr) == (a.v_new == nullptr), "decode: k_new and v_new must both be given or both be NULL");
+  MOA_REQUIRE(a.B > 0 && a.H > 0 && a.S > 0 && a.B <= 65535, "decode: bad shape");
+  if (a.k_new) MOA_REQUIRE(a.update_index && a.static_size, "decode: fused append needs update_index and static_size");
+  MOA_REQUIRE((a.rope_cos == nullptr) == (a.rope_sin == nullptr), "decode: rope_cos and rope_sin go together");
+  MOA_REQUIRE(a.rope_cos == nullptr || a.k_new != nullptr, "decode: the rotary embedding is applied in the fused-append mode only");
+  MOA_REQUIRE(aligned16(a.q) && a.q_bs % 8 == 0 && a.q_hs % 8 == 0 && a.q_bs >= 0 && a.q_hs >= 0,
+              "decode: q must be 16-byte aligned with strides that are multiples of 8 elements");
+  if (a.k_new)
+    MOA_REQUIRE(aligned16(a.k_new) && aligned16(a.v_new) && a.new_bs % 8 == 0 && a.new_hs % 8 == 0 && a.new_bs >= 0 &&
+                    a.new_hs >= 0,
+                "decode: k_new/v_new must be 16-byte aligned with strides that are multiples of 8 elements");
+  MOA_REQUIRE(aligned16(a.k_cache) && aligned16(a.v_cache), "decode: the caches must be 16-byte aligned");
+  MOA_REQUIRE(a.n_out_peers >= 0 && a.n_out_peers <= kMaxOutPeers && (a.n_out_peers == 0 || a.out_peers != nullptr),
+              "decode: at most 8 further output destinations");
+  int chunk = a.chunk;
+  if (chunk <= 0) chunk = auto_chunk(a.B, a.S);
+  const WsLayout w = ws_layout(a.B, a.H, a.D, a.S, chunk);
+  if (!a.workspace || a.workspace_bytes < w.total) {
     set_error_text("decode: workspace missing or smaller than moa_decode_workspace_bytes()");
     return MOA_ERR_WORKSPACE;
   }
   MOA_REQUIRE(w.nchunks <= 2147483647LL, "decode: too many chunks");
   DecodeParams p;
-  p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_new = k_new; p.v_new = v_new; p.out = out;
-  p.out_bs = out_bs; p.out_hs = out_hs; p.head_start = head_start; p.valid_len = valid_len;
-  p.update_index = update_index; p.mask_cache = mask_cache; p.static_size = static_size; p.kv_len = kv_len;
-  p.rope_cos = rope_cos; p.rope_sin = rope_sin;
-  p.B = B; p.H = H; p.S = S; p.scale_log2 = sm_scale * 1.4426950408889634f;
-  p.tickets = reinterpret_cast<int*>(workspace);
-  p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.ticket_bytes);
+  p.q = a.q; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.k_new = a.k_new; p.v_new = a.v_new; p.out = a.out;
+  p.out_bs = a.out_bs; p.out_hs = a.out_hs; p.q_bs = a.q_bs; p.q_hs = a.q_hs; p.new_bs = a.new_bs; p.new_hs = a.new_hs;
+  p.n_out_peers = a.n_out_peers;
+  for (int g = 0; g < kMaxOutPeers; ++g) p.out_peer[g] = g < a.n_out_peers ? a.out_peers[g] : nullptr;
+  for (int g = 0; g < a.n_out_peers; ++g) MOA_REQUIRE(p.out_peer[g] != nullptr, "decode: null output destination");
+  p.head_start = a.head_start; p.valid_len = a.valid_len;
+  p.update_index = a.update_index; p.mask_cache = a.mask_cache; p.static_size = a.static_size; p.kv_len = a.kv_len;
+  p.rope_cos = a.rope_cos; p.rope_sin = a.rope_sin;
+  p.B = a.B; p.H = a.H; p.S = a.S; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+  p.tickets = reinterpret_cast<int*>(a.workspace);
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a.workspace) + w.ticket_bytes);
   p.slots_per_batch = w.slots_per_batch; p.chunk = chunk;
-  dim3 grid((unsigned)w.nchunks, (unsigned)B);
-  if (dtype == MOA_F16) return launch_decode<__half>(p, D, grid, stream);
-  if (dtype == MOA_BF16) return launch_decode<__nv_bfloat16>(p, D, grid, stream);
+  dim3 grid((unsigned)w.nchunks, (unsigned)a.B);
+  if (a.dtype == MOA_F16) return launch_decode<__half>(p, a.D, a.out_f32 != 0, grid, a.stream);
+  if (a.dtype == MOA_BF16) return launch_decode<__nv_bfloat16>(p, a.D, a.out_f32 != 0, grid, a.stream);
   set_error_text("decode: dtype must be MOA_F16 or MOA_BF16");
   return MOA_ERR_UNSUPPORTED;
 }
 
 }  // namespace moa
+
+// The argument list shared by the decode entry points, in the order of include/moa_b200.h.
+#define MOA_DECODE_ARGS_DECL                                                                                       \
+  const void *q, void *k_cache, void *v_cache, const void *k_new, const void *v_new, void *out,                    \
+      int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride, int64_t new_head_stride,            \
+      int64_t out_batch_stride, int64_t out_head_stride, const int64_t *head_start, int64_t *valid_len,            \
+      int64_t *update_index, int64_t *mask_cache, const int64_t *static_size, int64_t kv_len, int B, int H, int D, \
+      int64_t S, float sm_scale, int dtype, int out_f32
+
+static moa::DecodeCall make_call(MOA_DECODE_ARGS_DECL, void* workspace, int64_t workspace_bytes, int chunk,
+                                 moa_stream_t stream) {
+  moa::DecodeCall a;
+  a.q = q; a.k_cache = k_cache; a.v_cache = v_cache; a.k_new = k_new; a.v_new = v_new; a.out = out;
+  a.q_bs = q_batch_stride; a.q_hs = q_head_stride; a.new_bs = new_batch_stride; a.new_hs = new_head_stride;
+  a.out_bs = out_batch_stride; a.out_hs = out_head_stride;
+  a.head_start = head_start; a.valid_len = valid_len; a.update_index = update_index; a.mask_cache = mask_cache;
+  a.static_size = static_size; a.kv_len = kv_len; a.B = B; a.H = H; a.D = D; a.S = S; a.sm_scale = sm_scale;
+  a.dtype = dtype; a.out_f32 = out_f32; a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.chunk = chunk;
+  a.stream = (cudaStream_t)stream; a.rope_cos = nullptr; a.rope_sin = nullptr; a.out_peers = nullptr; a.n_out_peers = 0;
+  return a;
+}
+#define MOA_DECODE_ARGS_PASS                                                                                     \
+  q, k_cache, v_cache, k_new, v_new, out, q_batch_stride, q_head_stride, new_batch_stride, new_head_stride,      \
+      out_batch_stride, out_head_stride, head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, \
+      H, D, S, sm_scale, dtype, out_f32
 
 extern "C" {
 
@@ -399,31 +484,31 @@ int moa_decode_workspace_init(void* workspace, int64_t workspace_bytes, moa_stre
   return MOA_OK;
 }
 
-int moa_decode_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new, void* out,
-                   int64_t out_batch_stride, int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
-                   int64_t* update_index, int64_t* mask_cache, const int64_t* static_size, int64_t kv_len, int B,
-                   int H, int D, int64_t S, float sm_scale, int dtype, void* workspace, int64_t workspace_bytes,
-                   int chunk, moa_stream_t stream) {
-  return moa::decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
-                                         head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H,
-                                         D, S, sm_scale, dtype, workspace, workspace_bytes, chunk,
-                                         (cudaStream_t)stream);
+int moa_decode_fwd(MOA_DECODE_ARGS_DECL, void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream) {
+  return moa::decode_launch_with_scratch(make_call(MOA_DECODE_ARGS_PASS, workspace, workspace_bytes, chunk, stream));
+}
+
+int moa_decode_rope_fwd(MOA_DECODE_ARGS_DECL, const void* rope_cos, const void* rope_sin, void* workspace,
+                        int64_t workspace_bytes, int chunk, moa_stream_t stream) {
+  MOA_REQUIRE(rope_cos && rope_sin && k_new && v_new, "decode_rope: needs k_new, v_new, rope_cos and rope_sin");
+  moa::DecodeCall a = make_call(MOA_DECODE_ARGS_PASS, workspace, workspace_bytes, chunk, stream);
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  return moa::decode_launch_with_scratch(a);
+}
+
+int moa_decode_gather_fwd(MOA_DECODE_ARGS_DECL, const void* rope_cos, const void* rope_sin, void* const* out_peers,
+                          int n_out_peers, void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream) {
+  MOA_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "decode_gather: rope_cos and rope_sin go together");
+  moa::DecodeCall a = make_call(MOA_DECODE_ARGS_PASS, workspace, workspace_bytes, chunk, stream);
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  a.out_peers = out_peers;
+  a.n_out_peers = n_out_peers;
+  return moa::decode_launch_with_scratch(a);
 }
 
 }  // extern "C"
-
-extern "C" int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
-                                   const void* rope_cos, const void* rope_sin, void* out, int64_t out_batch_stride,
-                                   int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
-                                   int64_t* update_index, int64_t* mask_cache, const int64_t* static_size,
-                                   int64_t kv_len, int B, int H, int D, int64_t S, float sm_scale, int dtype,
-                                   void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream) {
-  MOA_REQUIRE(rope_cos && rope_sin && k_new && v_new, "decode_rope: needs k_new, v_new, rope_cos and rope_sin");
-  return moa::decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
-                                         head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H,
-                                         D, S, sm_scale, dtype, workspace, workspace_bytes, chunk,
-                                         (cudaStream_t)stream, rope_cos, rope_sin);
-}
 
 // ------------------------------------------------------------------------------------------------
 // Decode entry point that brings its own scratch (no workspace argument, no allocation).
@@ -442,7 +527,6 @@ namespace {
 
 static __device__ __align__(256) unsigned char g_decode_scratch[MOA_DECODE_STATIC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
 void* g_decode_scratch_addr[kMaxDevices];  // device address of g_decode_scratch, per device ordinal
 std::mutex g_decode_scratch_mutex;
 
@@ -468,12 +552,7 @@ int decode_static_scratch(void** ptr) {
 }  // namespace
 }  // namespace moa
 
-extern "C" int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache, const void* k_new,
-                                     const void* v_new, void* out, int64_t out_batch_stride,
-                                     int64_t out_head_stride, const int64_t* head_start, int64_t* valid_len,
-                                     int64_t* update_index, int64_t* mask_cache, const int64_t* static_size,
-                                     int64_t kv_len, int B, int H, int D, int64_t S, float sm_scale, int dtype,
-                                     int chunk, moa_stream_t stream) {
+extern "C" int moa_decode_fwd_static(MOA_DECODE_ARGS_DECL, int chunk, moa_stream_t stream) {
   using namespace moa;
   MOA_REQUIRE(B > 0 && H > 0 && D > 0 && S > 0, "decode_static: bad shape");
   if (chunk <= 0) chunk = auto_chunk(B, S);
@@ -492,8 +571,6 @@ extern "C" int moa_decode_fwd_static(const void* q, void* k_cache, void* v_cache
   if (rc != MOA_OK) return rc;
   // The array keeps whatever the previous call left; the tickets must start at zero.
   MOA_CUDA_CHECK(cudaMemsetAsync(scratch, 0, (size_t)w.ticket_bytes, (cudaStream_t)stream));
-  return decode_launch_with_scratch(q, k_cache, v_cache, k_new, v_new, out, out_batch_stride, out_head_stride,
-                                    head_start, valid_len, update_index, mask_cache, static_size, kv_len, B, H, D,
-                                    S, sm_scale, dtype, scratch, MOA_DECODE_STATIC_SCRATCH_BYTES, chunk,
-                                    (cudaStream_t)stream);
+  return decode_launch_with_scratch(
+      make_call(MOA_DECODE_ARGS_PASS, scratch, MOA_DECODE_STATIC_SCRATCH_BYTES, chunk, stream));
 }

@@ -685,6 +685,15 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_arrive(&ctl->p_full[x][i & 1]);
     }
 
+    if (seen.total == 0 && (x == 0 || active1) && i_tok < p.N) {
+      // a tile that sees no key at all (no sink block and no window block): its rows are zero, like the rows
+      // of a visible tile whose own mask is empty
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+                      ((int64_t)b * p.o_sb + i_tok * p.o_sn + (int64_t)h * p.o_sh) * (OUT_F32 ? 4 : 2);
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+      for (int c = 0; c < DH * (OUT_F32 ? 4 : 2); c += 16) *reinterpret_cast<uint4*>(orow + c) = z;
+    }
     if (ok && seen.total > 0) {
       ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
       ok = __all_sync(0xffffffffu, ok);
@@ -791,10 +800,15 @@ template <typename T, bool F32, int DH>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
                    dim3 grid, cudaStream_t stream) {
   auto kern = moa_prefill_kernel<T, F32, DH>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
+  // The shared-memory opt-in is a per-device attribute of the function: keep the "done" flag per device
+  // ordinal (one process may drive several GPUs) and per instantiation.
+  constexpr int kMaxDevices = 64;
+  static bool configured[kMaxDevices];
+  int dev = -1;
+  MOA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
     MOA_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    configured = true;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
   kern<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   MOA_CUDA_CHECK(cudaGetLastError());

@@ -75,15 +75,15 @@ def test_every_chunk_size_gives_the_same_answer(chunk):
     out = torch.empty(B, 1, H, Dh, dtype=dtype, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
     for _ in range(2):  # second call reuses the workspace (tickets reset themselves)
-        rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), out.stride(0),
-                                     out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0, B, H, Dh, S, 0.09, 0,
-                                     ws.data_ptr(), need, chunk, stream)
+        rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), H * Dh, Dh, 0, 0,
+                                     out.stride(0), out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0,
+                                     B, H, Dh, S, 0.09, 0, 0, ws.data_ptr(), need, chunk, stream)
         assert rc == 0, _lib.lib.moa_last_error_detail()
         _close(out, ref, dtype, f"chunk={chunk}")
     # too small a workspace is refused, not overrun
-    rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), out.stride(0),
-                                 out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0, B, H, Dh, S, 0.09, 0,
-                                 ws.data_ptr(), need - 1, chunk, stream)
+    rc = _lib.lib.moa_decode_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0, 0, out.data_ptr(), H * Dh, Dh, 0, 0,
+                                 out.stride(0), out.stride(2), hsd.data_ptr(), vald.data_ptr(), 0, 0, 0, 0,
+                                 B, H, Dh, S, 0.09, 0, 0, ws.data_ptr(), need - 1, chunk, stream)
     assert rc == 4
 
 

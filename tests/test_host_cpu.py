@@ -25,14 +25,14 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(raw, name), f"{name} declared in include/moa_b200.h but not exported"
     assert declared == set(_lib.SYMBOLS)
-    assert _lib.lib.moa_abi_version() == 1
+    assert _lib.lib.moa_abi_version() == _lib.ABI_VERSION == 2
 
 
 def test_status_strings_and_argument_checks_without_gpu():
     lib = _lib.lib
     assert lib.moa_strerror(0) == b"ok"
     assert b"workspace" in lib.moa_strerror(4)
-    rc = lib.moa_decode_fwd(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 1, 128, 1, 1.0, 0, 0, 0, 0, 0)
+    rc = lib.moa_decode_fwd(*([0] * 6), *([0] * 6), *([0] * 5), 0, 1, 1, 128, 1, 1.0, 0, 0, 0, 0, 0, 0)
     assert rc == 1 and b"null pointer" in lib.moa_last_error_detail()
     rc = lib.moa_prefill_fwd(*([0] * 4), *([0] * 12), 0, 0, 1, 1, 64, 128, 1.0, 0, 0, 0, 0)
     assert rc == 1
