@@ -8,21 +8,21 @@ import torch
 import moa_b200
 from moa_b200 import _lib
 from oracle import moa_oracle as orc
+import parity
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
-# fp16: the tolerance the project states (max-abs 2e-3, mean-rel 1e-3 against fp32).
-# bf16: the store alone costs about one bf16 ulp (7.8e-3 at |x|~1, ~1.4e-3 mean-rel), so the bound is wider.
-TOL = {torch.float16: (2e-3, 1e-3), torch.bfloat16: (1.6e-2, 4e-3)}
+# fp16 results and the fp32-store mode of the bf16 kernel are held to the tolerance the project states
+# (max-abs 2e-3, mean-rel 1e-3 against fp32).  A bf16 *store* alone costs up to half a bf16 ulp
+# (3.9e-3 at |x| in [1, 2), about 1.4e-3 mean-rel), so bf16 outputs are checked two ways: they must be
+# exactly the rounding of the fp32-store result, and they get the wider bound below against the oracle.
+TOL = {torch.float16: (parity.MAX_ABS, parity.MEAN_REL), torch.bfloat16: (1.6e-2, 4e-3)}
 
 
 def _close(out, ref, dtype, what=""):
-    out, ref = out.float().cpu(), ref.float().cpu()
-    max_abs = (out - ref).abs().max().item()
-    mean_rel = ((out - ref).abs().mean() / ref.abs().mean().clamp_min(1e-12)).item()
-    a, r = TOL[dtype]
-    assert max_abs <= a and mean_rel <= r, f"{what}: max-abs {max_abs:.3e} mean-rel {mean_rel:.3e}"
+    a, r = TOL[dtype] if out.dtype != torch.float32 else (parity.MAX_ABS, parity.MEAN_REL)
+    parity.check(out, ref, a, r, f"{what} [{str(dtype)[6:]} in, {str(out.dtype)[6:]} out]")
 
 
 def _random_cache(B, caps, Dh, dtype, gen, full=False):
@@ -58,6 +58,12 @@ def test_sparse_decode_matches_oracle(dtype, Dh, caps):
     _close(out, ref, dtype, f"caps={caps}")
     # heads with nothing valid give zeros, not NaN
     assert torch.isfinite(out.float()).all()
+    # fp32-store mode: same math, unrounded result, held to the stated tolerance for both dtypes;
+    # the 16-bit output is exactly its rounding
+    out32 = moa_b200.sparse_decode(q.cuda(), k.cuda(), v.cuda(), hs.cuda(), valid.cuda(), sm, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    _close(out32, ref, dtype, f"caps={caps}")
+    assert torch.equal(out32.to(dtype), out)
 
 
 @pytest.mark.parametrize("chunk", [64, 96, 128, 256, 1000, 100000])
@@ -277,3 +283,67 @@ def test_fused_decode_leaves_other_slots_alone():
             assert torch.equal(kc[b, slot], k1[b, h, 0]) and torch.equal(cache.value_cache[0][b, slot], v1[b, h, 0])
     for big in (big_k, big_v):                                         # nothing outside the cache's own rows
         assert (big[:pad] == marker).all() and (big[pad + B * S:] == marker).all()
+
+
+def test_config4_shape_multi_chunk_merge_bf16():
+    """The decode shape of config 4 of BASELINE.json at reduced batch and head count: bf16, head_dim 128,
+    8 heads with windows drawn from U[1k, 16k] (rounded up to 64) plus 64 sinks, batch 4, rings filled from a
+    prompt longer than the largest ring, three fused decode steps, with the 2048-row chunk the library picks
+    at config 4's full batch: every head is split over several blocks and the last-arriver merge combines up
+    to eight partial records per head.  Checked per step: the fp32-store
+    output against the fp32 oracle at the stated tolerance, the bf16 output as exactly its rounding, and the
+    ring state bit-exactly."""
+    rng = np.random.RandomState(4000)
+    B, H, Dh = 4, 8, 128
+    caps = [64 + int(-(-int(w) // 64) * 64) for w in rng.uniform(1024, 16384, H)]
+    N = max(caps) + 100
+    gen = torch.Generator().manual_seed(4001)
+    dtype = torch.bfloat16
+    # the oracle keeps bf16 values exactly in float32 (numpy has no bf16)
+    o = orc.RingCacheOracle([caps], [[64] * H], B, Dh, dtype=np.float32)
+    c = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", dtype)
+    c.decode_chunk = 2048      # what the library chooses at config 4's full batch of 64
+    k = torch.randn(B, H, N, Dh, generator=gen).to(dtype)
+    v = torch.randn(B, H, N, Dh, generator=gen).to(dtype)
+    o.update(k.float().numpy(), v.float().numpy(), 0)
+    c.update(k.cuda(), v.cuda(), 0)
+    del k, v
+    assert np.array_equal(c.key_cache[0].float().cpu().numpy(), o.key_cache[0])
+    sm = Dh ** -0.5
+    for step in range(3):
+        q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen).to(dtype) for _ in range(3))
+        kc, vc = o.update(k1.float().numpy(), v1.float().numpy(), 0)
+        ref = orc.decode_attention_fp32(q, torch.from_numpy(kc), torch.from_numpy(vc),
+                                        torch.from_numpy(o.cache_head_start_index[0]),
+                                        torch.from_numpy(o.cache_valid_length[0]), sm)
+        # same step twice from the same state: fp32 store, then (state restored) bf16 store
+        state = (c.cache_update_index[0].clone(), c.cache_valid_length[0].clone(), c.mask_cache[0].clone(), c._kv_len[0],
+                 c.cache_position)
+        out32 = c.decode_attention(q.cuda(), k1.cuda(), v1.cuda(), 0, sm, out_dtype=torch.float32)
+        c.cache_update_index[0].copy_(state[0]); c.cache_valid_length[0].copy_(state[1]); c.mask_cache[0].copy_(state[2])
+        c._kv_len[0], c.cache_position = state[3], state[4]
+        out16 = c.decode_attention(q.cuda(), k1.cuda(), v1.cuda(), 0, sm)
+        _close(out32, ref, dtype, f"config-4 shape, step {step}")
+        _close(out16, ref, dtype, f"config-4 shape, step {step}")
+        assert torch.equal(out32.to(dtype), out16)
+        assert np.array_equal(c.cache_update_index[0].cpu().numpy(), o.cache_update_index[0])
+        assert np.array_equal(c.cache_valid_length[0].cpu().numpy(), o.cache_valid_length[0])
+    assert np.array_equal(c.key_cache[0].float().cpu().numpy(), o.key_cache[0])
+    assert np.array_equal(c.value_cache[0].float().cpu().numpy(), o.value_cache[0])
+
+
+def test_heads_without_rows_get_zero_output():
+    """Two heads share a start index, so the first of them owns no rows: its output row is defined (zeros)."""
+    gen = torch.Generator().manual_seed(5)
+    B, Dh = 2, 128
+    caps = [128, 0, 192]
+    S = sum(caps)
+    k = torch.randn(B, S, Dh, generator=gen).half()
+    v = torch.randn(B, S, Dh, generator=gen).half()
+    hs = torch.tensor([[0, 128, 128]] * B, dtype=torch.int64)
+    valid = torch.tensor([[128, 0, 192]] * B, dtype=torch.int64)
+    q = torch.randn(B, 3, 1, Dh, generator=gen).half()
+    out = torch.full((B, 1, 3, Dh), float("nan"), dtype=torch.float16, device="cuda")
+    moa_b200.sparse_decode(q.cuda(), k.cuda(), v.cuda(), hs.cuda(), valid.cuda(), 0.1, out=out)
+    assert torch.isfinite(out).all() and out[:, :, 1].abs().sum() == 0
+    _close(out, orc.decode_attention_fp32(q, k, v, hs, valid, 0.1), torch.float16, "zero-capacity head")

@@ -214,3 +214,128 @@ def test_flashinfer_compat_calls_like_the_reference_call_sites():
     want = orc.decode_attention_fp32(qd.transpose(1, 2), kc, vc, starts, valid, D ** -0.5)
     assert got.shape == (B, 1, H, D)
     assert (got.float().cpu() - want).abs().max() <= 2e-3
+
+
+def test_fused_qkv_views_give_the_same_result_as_separate_contiguous_projections():
+    """The kernels read q, k, v through strides out of the single projection GEMM's output; the result must be
+    bit-identical to feeding them contiguous copies of the same values (prefill and fused decode)."""
+    gen = torch.Generator().manual_seed(23)
+    B, H, D, N = 2, 3, 128, 200
+    caps = [128, 192, 320]
+    qkv = torch.randn(B, N, 3, H, D, generator=gen).half().cuda()
+    qv, kv, vv = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    assert not qv.is_contiguous()
+    sb = torch.tensor([1, 1, 1], dtype=torch.int32).cuda()
+    lb = torch.tensor([1, 2, 4], dtype=torch.int32).cuda()
+    a = moa_b200.sparse_prefill(qv, kv, vv, 0.1, sb, lb)
+    b = moa_b200.sparse_prefill(qv.contiguous(), kv.contiguous(), vv.contiguous(), 0.1, sb, lb)
+    moa_b200.check_device_status()
+    assert torch.equal(a, b)
+    c1 = moa_b200.StaticCircularCache([caps], B, D, [[64] * H], "cuda", torch.float16)
+    c2 = moa_b200.StaticCircularCache([caps], B, D, [[64] * H], "cuda", torch.float16)
+    c1.update(kv, vv, 0)
+    c2.update(kv.contiguous(), vv.contiguous(), 0)
+    assert torch.equal(c1.key_cache[0], c2.key_cache[0]) and torch.equal(c1.value_cache[0], c2.value_cache[0])
+    step = torch.randn(B, 1, 3, H, D, generator=gen).half().cuda()
+    q1, k1, v1 = (step[:, :, i].transpose(1, 2) for i in range(3))
+    cos, sin = moa_b200.module.rotary_cos_sin(torch.full((B, 1), N).cuda(), D, 10000.0, torch.float16)
+    o1 = c1.decode_attention(q1, k1, v1, 0, 0.1, rope=(cos, sin))
+    o2 = c2.decode_attention(q1.contiguous(), k1.contiguous(), v1.contiguous(), 0, 0.1, rope=(cos, sin))
+    assert torch.equal(o1, o2) and torch.equal(c1.key_cache[0], c2.key_cache[0])
+    assert torch.equal(c1.cache_update_index[0], c2.cache_update_index[0])
+
+
+def test_adopted_huggingface_llama_reproduces_its_own_dense_forward():
+    """`update_model_function` on a loaded HuggingFace Llama model, with a plan whose windows cover the whole
+    context: the logits of the prefill and of the following decode steps must agree with the model's own
+    dense causal forward (its own attention, its own cache)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=4, vocab_size=300, max_position_embeddings=2048, rope_theta=10000.0,
+                      rms_norm_eps=1e-5, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = LlamaForCausalLM(cfg).half().eval().cuda()
+    model = moa_b200.update_model_function(hf, "meta-llama/Llama-2-7b-hf")
+    plan = {"alphas": [[100000.0] * 4] * 2, "betas": [[0.0] * 4] * 2}
+    model.model.set_mixture_of_attention(plan, permute_head=False, moa_max_new_token=64, last_hidden_only=False)
+    ids = torch.randint(0, 300, (2, 200), device="cuda")
+    with torch.no_grad():
+        ref = hf(input_ids=ids, use_cache=True)
+    logits, cache = model(ids)
+    assert logits.shape == ref.logits.shape == (2, 200, 300)
+    a, r = _rel(logits, ref.logits)
+    assert r < 1e-2, ("prefill", a, r)
+    past = ref.past_key_values
+    for step in range(3):
+        nxt = torch.randint(0, 300, (2, 1), device="cuda")
+        with torch.no_grad():
+            ref = hf(input_ids=nxt, past_key_values=past, use_cache=True)
+        past = ref.past_key_values
+        logits, cache = model(nxt, past_key_values=cache)
+        a, r = _rel(logits, ref.logits)
+        assert logits.shape == (2, 1, 300) and r < 1e-2, (step, a, r)
+
+
+def test_head_sharded_model_on_one_gpu_equals_unsharded():
+    """Two head-shard replicas of the model run as two host threads on one GPU; the gather between them is a
+    host-side exchange with the same contract as `HeadSharding.all_gather` (shards concatenated in shard
+    order).  Prefill and decode outputs must equal the unsharded model's."""
+    import threading
+    plan = {"alphas": [[1024.0, 128.0, 512.0, 128.0], [256.0, 256.0, 64.0, 2048.0]],
+            "betas": [[0.0, 0.25, 0.0, 0.5], [0.125, 0.0, 0.5, 0.0]]}
+    ids = torch.randint(0, 100, (2, 300), device="cuda")
+    nxt = [torch.randint(0, 100, (2, 1), device="cuda") for _ in range(3)]
+    full = _tiny_model(5)
+    full.set_mixture_of_attention(plan, moa_max_new_token=64)
+    want = []
+    h, c = full(ids)
+    want.append(h)
+    for t in nxt:
+        h, c = full(t, past_key_values=c)
+        want.append(h)
+    torch.cuda.synchronize()
+
+    world = 2
+    slots, barrier, got, errors = [None] * world, threading.Barrier(world), [[] for _ in range(world)], []
+
+    def exchange(rank):
+        def gather(local):
+            torch.cuda.synchronize()
+            slots[rank] = local
+            barrier.wait()
+            out = torch.cat(list(slots), dim=2)
+            torch.cuda.synchronize()
+            barrier.wait()
+            return out
+        return gather
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(0)
+            m = _tiny_model(5)
+            m.set_mixture_of_attention(plan, moa_max_new_token=64)
+            m.shard_heads(world, rank, seq_len=300)
+            for layer in m.layers:
+                layer.self_attn.gather = exchange(rank)
+            assert [len(c) for c in m.new_cache(2, 300).cache_max_length] == [2, 2]
+            h, c = m(ids)
+            got[rank].append(h)
+            for t in nxt:
+                h, c = m(t, past_key_values=c)
+                got[rank].append(h)
+            torch.cuda.synchronize()
+        except Exception as exc:          # a failed rank must not leave the other one waiting
+            errors.append((rank, repr(exc)))
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    for rank in range(world):
+        assert len(got[rank]) == len(want)
+        for i, (g, w) in enumerate(zip(got[rank], want)):
+            a, r = _rel(g, w)
+            assert a < 2e-2 and r < 1e-2, (rank, i, a, r)

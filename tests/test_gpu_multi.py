@@ -71,3 +71,31 @@ def test_two_gpu_head_sharded_decode_equals_single_gpu():
         mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
         # shards chunk the flattened cache differently: equal up to the rounding of the fp16 store
         assert len(ret) == world and all(v <= 1e-3 for v in ret.values()), dict(ret)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_driving_two_gpus():
+    """The reference's own multi-GPU mode is one process with layers on several devices (device_map="auto";
+    its cache materialises each layer on that layer's device).  Per-device launch state (the prefill kernel's
+    shared-memory opt-in, the decode kernel's grid sizing) must therefore be kept per device."""
+    import moa_b200
+    from oracle import moa_oracle as orc
+    gen = torch.Generator().manual_seed(31)
+    q, k, v = (torch.randn(1, 2, 300, 128, generator=gen).half() for _ in range(3))
+    ref = orc.prefill_attention_fp32(q, k, v, 0.1, [1, 1], [1, 3])
+    caps = [128, 320]
+    S = sum(caps)
+    kc, vc = (torch.randn(2, S, 128, generator=gen).half() for _ in range(2))
+    qd = torch.randn(2, 2, 1, 128, generator=gen).half()
+    starts = torch.tensor([[0, 128]] * 2)
+    valid = torch.tensor([[128, 320], [100, 7]])
+    dref = orc.decode_attention_fp32(qd, kc, vc, starts, valid, 0.1)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        sb = torch.tensor([1, 1], dtype=torch.int32, device=dev)
+        lb = torch.tensor([1, 3], dtype=torch.int32, device=dev)
+        out = moa_b200.sparse_prefill(q.to(dev), k.to(dev), v.to(dev), 0.1, sb, lb)
+        moa_b200.check_device_status(dev)
+        assert out.device == torch.device(dev)
+        assert (out.float().cpu() - ref).abs().max() <= 2e-3, dev
+        got = moa_b200.sparse_decode(qd.to(dev), kc.to(dev), vc.to(dev), starts.to(dev), valid.to(dev), 0.1)
+        assert (got.float().cpu() - dref).abs().max() <= 2e-3, dev

@@ -134,3 +134,73 @@ def test_flashinfer_compat_exports_the_names_the_reference_imports():
         "q", "k", "v", "causal", "num_global_blocks", "num_band_blocks", "kv_layout"]
     assert list(inspect.signature(fi.moa_decode).parameters) == [
         "q", "k", "v", "head_start_index", "head_valid_length", "sm_scale"]
+
+
+def _tiny_hf_llama(tie=False):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=2,
+                      num_key_value_heads=2, vocab_size=128, max_position_embeddings=512, rope_theta=10000.0,
+                      rms_norm_eps=1e-5, tie_word_embeddings=tie)
+    torch.manual_seed(0)
+    return LlamaForCausalLM(cfg).half().eval()
+
+
+def test_llama_checkpoint_state_dict_loads_as_it_is():
+    """Parameter names are those of a HuggingFace Llama checkpoint (`model.layers.N.mlp.*`, `lm_head`), so the
+    plan the offline pipeline produces can be run on real weights."""
+    hf = _tiny_hf_llama()
+    m = moa_b200.MoALlamaForCausalLM.from_config(hf.config.to_dict())
+    attn = m.model.layers[0].self_attn
+    fused = attn.fused_qkv_weight()                         # the three projections now alias one tensor
+    result = m.load_state_dict(hf.state_dict(), strict=True)
+    assert not result.missing_keys and not result.unexpected_keys
+    assert attn.fused_qkv_weight() is fused                 # loading copied in place, the aliasing survived
+    hf_attn = hf.model.layers[0].self_attn
+    assert torch.equal(fused, torch.cat([hf_attn.q_proj.weight, hf_attn.k_proj.weight, hf_attn.v_proj.weight]))
+    assert m.model.norm.eps == 1e-5 and m.model.rope_theta == 10000.0
+    assert torch.equal(m.lm_head.weight, hf.lm_head.weight)
+
+
+def test_update_model_function_adopts_a_loaded_model_without_copying():
+    hf = _tiny_hf_llama()
+    m = moa_b200.update_model_function(hf, "meta-llama/Llama-2-7b-hf")
+    assert isinstance(m, moa_b200.MoALlamaForCausalLM) and hasattr(m.model, "set_mixture_of_attention")
+    assert m.model.layers[1].mlp.down_proj.weight.data_ptr() == hf.model.layers[1].mlp.down_proj.weight.data_ptr()
+    assert moa_b200.update_model_function(m, "llama") is m
+    tied = moa_b200.update_model_function(_tiny_hf_llama(tie=True), "vicuna")
+    assert tied.lm_head.weight.data_ptr() == tied.model.embed_tokens.weight.data_ptr()
+    with pytest.raises(NotImplementedError):
+        moa_b200.update_model_function(hf, "mistral-7b")
+    # a head permutation replaces the projection weights; the fused weight follows
+    m.set_mixture_of_attention({"alphas": [[1024.0, 128.0]] * 2, "betas": [[0.0, 0.0]] * 2}, permute_head=True)
+    attn, hf_attn = m.model.layers[0].self_attn, hf.model.layers[0].self_attn
+    D = 128
+    assert torch.equal(attn.fused_qkv_weight()[:D], hf_attn.q_proj.weight[D:])           # head 1 first now
+    assert torch.equal(attn.o_proj.weight[:, :D], hf_attn.o_proj.weight[:, D:])
+
+
+def test_model_head_sharding_slices_weights_and_plan():
+    plan_ = {"alphas": [[128.0, 1024.0, 512.0, 256.0]] * 2, "betas": [[0.0, 0.2, 0.0, 0.1]] * 2}
+    torch.manual_seed(3)
+    ref = moa_b200.MoALlamaModel(2, 64, 4, 128, vocab_size=50, dtype=torch.float32)
+    full_q = ref.layers[0].self_attn.q_proj.weight.data.clone()
+    full_o = ref.layers[0].self_attn.o_proj.weight.data.clone()
+    seen = []
+    for rank in range(2):
+        torch.manual_seed(3)
+        m = moa_b200.MoALlamaModel(2, 64, 4, 128, vocab_size=50, dtype=torch.float32)
+        m.set_mixture_of_attention(plan_, moa_max_new_token=0)
+        m.shard_heads(2, rank, seq_len=4096)
+        sh = m.head_shardings[0]
+        attn = m.layers[0].self_attn
+        assert attn.num_local_heads == 2 and attn.q_proj.weight.shape == (32, 64)
+        assert attn.fused_qkv_weight().shape == (96, 64)
+        for i, h in enumerate(sh.local_heads):                        # rows of the local heads, in shard order
+            assert torch.equal(attn.q_proj.weight[16 * i:16 * (i + 1)], full_q[16 * h:16 * (h + 1)])
+        for i, h in enumerate(sh.order):                              # o_proj columns follow the gathered order
+            assert torch.equal(attn.o_proj.weight[:, 16 * i:16 * (i + 1)], full_o[:, 16 * h:16 * (h + 1)])
+        assert m.local_moa_config["alphas"][0] == [plan_["alphas"][0][h] for h in sh.local_heads]
+        seen += sh.local_heads
+        with pytest.raises(AssertionError):
+            m.shard_heads(2, rank, seq_len=4096)
+    assert sorted(seen) == [0, 1, 2, 3]
