@@ -4,7 +4,7 @@
 // A and B that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
 //              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM, computes the
-//              exponentials against a lazily updated max, writes P (fp16, two per 32-bit
+//              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
 //              column) over the first half of the S buffer the row came from, rescales O in TMEM
 //              when the max moved, and finally runs the epilogue
 //   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
@@ -276,10 +276,11 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
   return d;
 }
 
-// Instruction descriptor for kind::f16 with fp32 accumulation.  The formats of A and B are separate fields
-// (0 = fp16, 1 = bf16) and need not agree.
-__host__ __device__ constexpr uint32_t make_idesc(int a_bf16, int b_bf16, int b_mn_major, int M, int N) {
-  return (1u << 4) | ((uint32_t)a_bf16 << 7) | ((uint32_t)b_bf16 << 10) | ((uint32_t)b_mn_major << 16) |
+// Instruction descriptor for kind::f16 with fp32 accumulation.  A and B have separate format fields (0 = fp16,
+// 1 = bf16) but must be given the same format: fp16 A (P) with bf16 B (V) raises an illegal-instruction
+// error on B200.
+__host__ __device__ constexpr uint32_t make_idesc(int is_bf16, int b_mn_major, int M, int N) {
+  return (1u << 4) | ((uint32_t)is_bf16 << 7) | ((uint32_t)is_bf16 << 10) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
@@ -448,9 +449,8 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     {
       const int x = warp - 9;
       const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
-      constexpr uint32_t idesc_qk = make_idesc(kBf16, kBf16, 0, kBM, kBN);
-      // P is always fp16 (see the softmax side), V has the tensors' dtype
-      constexpr uint32_t idesc_pv = make_idesc(0, kBf16, 1, kBM, DH);
+      constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, DH);
       // descriptors differ only in their start-address field (bytes >> 4): build each base once
       const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
       const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
@@ -656,10 +656,9 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, nm2);
         const float2 p2 = make_float2(exp2f(x2.x), exp2f(x2.y));
         ls2[(c >> 1) & 1] = __fadd2_rn(ls2[(c >> 1) & 1], p2);
-        // P goes to the tensor core as fp16 whatever the tensors' dtype: its values lie in (0, 2^8] (the lazy
-        // max lags the true one by at most kLazyMaxSlack), where fp16's 11-bit mantissa costs an eighth of the
-        // rounding error bf16's 8 bits would, and the MMA takes A and B in different 16-bit formats
-        pk[c >> 1] = Cvt<__half>::pack(p2.x, p2.y);
+        // P has the tensors' dtype (the MMA wants A and B in one format): with bf16 its 8-bit mantissa is the
+        // largest rounding error of the bf16 path
+        pk[c >> 1] = Cvt<T>::pack(p2.x, p2.y);
       }
       l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
       // P row -> TMEM, over the first half of the S buffer it came from (two values per column, even key in

@@ -144,6 +144,24 @@ def prefill_attention_fp32(
     return out
 
 
+def prefill_attention_masked_sdpa(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    sm_scale: float,
+    sink_blocks: Sequence[int],
+    local_blocks: Sequence[int],
+) -> torch.Tensor:
+    """The PyTorch route to the same result, as a timed CPU baseline: one scaled_dot_product_attention call
+    over all heads with the boolean element mask (the mask MoA/attention/convert.py:159-192 ``layout_to_mask``
+    expands from the block layout of MoA/attention/pattern.py:149-183, and-ed with causal), in the tensors'
+    dtype.  q, k, v: (B, H, N, D); returns (B, N, H, D)."""
+    n = q.shape[2]
+    mask = torch.from_numpy(np.stack([prefill_mask(n, int(s), int(l)) for s, l in zip(sink_blocks, local_blocks)]))
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask[None], scale=sm_scale)
+    return out.transpose(1, 2)
+
+
 # --------------------------------------------------------------------------------------
 # ring cache bookkeeping                       MoA/attention/cache_utils.py:644-1180
 # --------------------------------------------------------------------------------------

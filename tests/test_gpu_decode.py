@@ -14,10 +14,11 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 # fp16 results and the fp32-store mode of the bf16 kernel are held to the tolerance the project states
-# (max-abs 2e-3, mean-rel 1e-3 against fp32).  A bf16 *store* alone costs up to half a bf16 ulp
-# (3.9e-3 at |x| in [1, 2), about 1.4e-3 mean-rel), so bf16 outputs are checked two ways: they must be
-# exactly the rounding of the fp32-store result, and they get the wider bound below against the oracle.
-TOL = {torch.float16: (parity.MAX_ABS, parity.MEAN_REL), torch.bfloat16: (1.6e-2, 4e-3)}
+# (max-abs 2e-3, mean-rel 1e-3 against fp32); measured: fp16 about 1.2e-4 / 1.8e-4, bf16 with fp32 store
+# about 5e-7 / 5e-7.  A bf16 *store* alone costs up to half a bf16 ulp (3.9e-3 at |x| in [1, 2), about
+# 1.4e-3 mean-rel), so bf16 outputs are checked two ways: they must be exactly the rounding of the fp32-store
+# result, and against the oracle they get 1.5 x the worst error measured over these tests (5.8e-3 / 1.5e-3).
+TOL = {torch.float16: (parity.MAX_ABS, parity.MEAN_REL), torch.bfloat16: (9e-3, 2.3e-3)}
 
 
 def _close(out, ref, dtype, what=""):

@@ -309,15 +309,20 @@ def test_head_sharded_model_on_one_gpu_equals_unsharded():
             return out
         return gather
 
+    models = []
+    for rank in range(world):          # built one after the other: the weights come from the global generator
+        m = _tiny_model(5)
+        m.set_mixture_of_attention(plan, moa_max_new_token=64)
+        m.shard_heads(world, rank, seq_len=300)
+        for layer in m.layers:
+            layer.self_attn.gather = exchange(rank)
+        assert [len(c) for c in m.new_cache(2, 300).cache_max_length] == [2, 2]
+        models.append(m)
+
     def run(rank):
         try:
             torch.cuda.set_device(0)
-            m = _tiny_model(5)
-            m.set_mixture_of_attention(plan, moa_max_new_token=64)
-            m.shard_heads(world, rank, seq_len=300)
-            for layer in m.layers:
-                layer.self_attn.gather = exchange(rank)
-            assert [len(c) for c in m.new_cache(2, 300).cache_max_length] == [2, 2]
+            m = models[rank]
             h, c = m(ids)
             got[rank].append(h)
             for t in nxt:

@@ -13,6 +13,14 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
+# The fp32-store mode of the bf16 kernel: P goes to the tensor core as bf16 (the MMA takes A and B in one
+# format only), and its 8-bit mantissa bounds the accuracy whatever the store does: a relative rounding error
+# of up to 2^-9 per weight gives about 1.2e-3 - 1.7e-3 mean-rel on N(0,1) data.  Worst measured over these
+# tests: max-abs 3.8e-3, mean-rel 1.70e-3 (config 3 at full length: 3.1e-3 / 1.70e-3); the bound is 1.5 x that.
+# The bf16 store is checked to be exactly the rounding of the fp32-store result.
+BF16_F32_STORE = (5.7e-3, 2.6e-3)
+
+
 def _close(out, ref, what="", max_abs=parity.MAX_ABS, mean_rel=parity.MEAN_REL):
     parity.check(out, ref, max_abs, mean_rel, f"{what} [{str(out.dtype)[6:]} out]")
 
@@ -126,14 +134,13 @@ def test_bf16_fp32_store_meets_the_tolerance_and_bf16_store_is_its_rounding():
     ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b)
     out32 = _run(q, k, v, sm, sink_b, local_b, out_dtype=torch.float32)
     assert out32.dtype == torch.float32
-    # identical math with the accumulator stored unrounded: held to the tolerance stated for fp16 (P goes to
-    # the tensor core as fp16 in both kernels); the bf16 output is exactly the rounding of this result and
-    # therefore within half a bf16 ulp of it
-    _close(out32, ref, "bf16 inputs, fp32 store")
+    # identical math with the accumulator stored unrounded; the bf16 output is exactly the rounding of this
+    # result and therefore within half a bf16 ulp of it
+    _close(out32, ref, "bf16 inputs, fp32 store", *BF16_F32_STORE)
     out16 = _run(q, k, v, sm, sink_b, local_b)
     assert out16.dtype == torch.bfloat16
     assert torch.equal(out16.cpu(), out32.cpu().bfloat16())
-    _close(out16, ref, "bf16 inputs, bf16 store", 1.6e-2, 4e-3)
+    _close(out16, ref, "bf16 inputs, bf16 store", 1e-2, 3.1e-3)      # measured 6.4e-3 / 2.1e-3
 
 
 def test_config0_full_size():
@@ -190,7 +197,7 @@ def test_many_heads_all_sms_busy_with_spot_rows():
     qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
     for a, b in [(0, 128), (4000, 4128), (N - 128, N)]:
         ref = orc.prefill_attention_fp32(qc, kc, vc, sm, sink_b, local_b, row_range=(a, b))
-        _close(out[:, a:b], ref, f"32 heads x 8192 bf16, fp32 store, rows {a}:{b}")
+        _close(out[:, a:b], ref, f"32 heads x 8192 bf16, fp32 store, rows {a}:{b}", *BF16_F32_STORE)
 
 
 def test_constant_value_property_full_length():
@@ -231,7 +238,7 @@ def test_config3_full_length_spot_rows():
     qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
     for a, b in [(0, 128), (32768 - 64, 32768 + 64), (N - 128, N)]:
         ref = orc.prefill_attention_fp32(qc, kc, vc, sm, sink_b, local_b, row_range=(a, b))
-        _close(out32[:, a:b], ref, f"config 3 full length, local blocks {local_b}, rows {a}:{b}")
+        _close(out32[:, a:b], ref, f"config 3 full length, local blocks {local_b}, rows {a}:{b}", *BF16_F32_STORE)
         assert torch.equal(out16[:, a:b].cpu(), out32[:, a:b].cpu().bfloat16())
 
 
@@ -289,7 +296,7 @@ def test_head_dim_64(dtype):
         _close(out, ref, "D=64 fp16")
     else:
         out32 = _run(q, k, v, sm, sink_b, local_b, out_dtype=torch.float32)
-        _close(out32, ref, "D=64 bf16, fp32 store")
+        _close(out32, ref, "D=64 bf16, fp32 store", *BF16_F32_STORE)
         out16 = _run(q, k, v, sm, sink_b, local_b)
         assert torch.equal(out16.cpu(), out32.cpu().bfloat16())
 
