@@ -531,10 +531,19 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
     out = torch.empty(Bl, 1, len(mine), Dl, dtype=torch.bfloat16, device=device)
     sm = Dl ** -0.5
 
-    # correctness probe, outside the timed regions: one step from the known state, gathered; rank 0 recomputes
-    # one head of its own and one of the last rank's with the fp32 oracle on its CPU (2 batch rows)
+    # correctness probe, outside the timed regions: one step from the known state, gathered (with N > 1 once
+    # through the NCCL all-gather and once, from the same state, through the fused peer-store gather); rank 0
+    # recomputes one head of its own and one of the last rank's with the fp32 oracle on its CPU (2 batch rows)
     cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
     gathered = sh.all_gather(out).clone()
+    pg = None
+    fused_equal = None
+    if world > 1:
+        pg = moa_b200.PeerGather(sh, Bl, Dl, torch.bfloat16, device)
+        fill_rings_directly(cache, 0, device, mine_ids, 131072, 4000)
+        fused = pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
+        pg.check()
+        fused_equal = bool(torch.equal(fused, gathered))
     probe = None
     if rank == 0:
         worst = 0.0
@@ -557,13 +566,20 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
         cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
         sh.all_gather(out)
 
+    def step_fused(i):
+        pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
+
+    variants = [("attention_only", step_attention), ("attention_allgather", step)]
+    if pg is not None:
+        variants.append(("attention_peer_gather", step_fused))
     res = {}
-    for name, fn in (("attention_only", step_attention), ("attention_allgather", step)):
+    for name, fn in variants:
         for i in range(warmup):
             fn(i)
         ms, _ = time_blocks(fn, steps, device, dist, min_blocks=5, min_region_s=0.1)
         res[name + "_us"] = statistics.median(ms) / steps * 1e3
-    us = res["attention_allgather_us"]
+    us_nccl = res["attention_allgather_us"]
+    us = res.get("attention_peer_gather_us", us_nccl)
 
     # The step after attention: o_proj (hidden 8192) in its gathered and its row-parallel form.
     hidden = Hl * Dl
@@ -579,27 +595,40 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
         cache.decode_attention(trio[0], trio[1], trio[2], 0, sm, out=out)
         sh.output_projection(out, w_loc, mode="row_parallel")
 
+    def step_fused_proj(i):
+        full = pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
+        torch.nn.functional.linear(full.view(Bl, 1, Hl * Dl), w_full)
+
     proj = {}
-    for name, fn in (("gather", step_gather), ("row_parallel", step_row)):
+    for name, fn in (("gather", step_gather), ("row_parallel", step_row)) + \
+            ((("peer_gather", step_fused_proj),) if pg is not None else ()):
         for i in range(warmup):
             fn(i)
         ms, _ = time_blocks(fn, steps, device, dist, min_blocks=5, min_region_s=0.1)
         proj[name + "_us"] = statistics.median(ms) / steps * 1e3
+    if pg is not None:
+        pg.check()
+        pg.close()
 
     kv_bytes_all = moa_b200.decode_bytes(Bl, caps, Dl, 2)
     loads = [sum(caps[h] for h in s) for s in sh.shards]
     return {"workload": "config4 one layer, attention + gather of the head shards: B64 H64 D128 bf16, windows "
                         f"U[1k,16k] + 64 sinks, heads sharded over {world} GPU(s)", "us_per_step": us,
             "tokens_per_s": Bl / (us * 1e-6), "aggregate_hbm_gbs": kv_bytes_all / (us * 1e-6) / 1e9,
+            "gather": "decode kernel stores its rows into every rank's buffer over NVLink + barrier kernel" if pg is not None
+                      else "none (one GPU)",
             "breakdown_us": {"attention_kernel": res["attention_only_us"],
-                             "gather_and_copy": us - res["attention_only_us"]},
+                             "peer_store_gather_and_barrier": us - res["attention_only_us"],
+                             "nccl_allgather_and_copy": us_nccl - res["attention_only_us"]},
+            "us_per_step_nccl_allgather": us_nccl,
+            "fused_gather_equals_nccl_gather": fused_equal,
             "allgather_bytes_per_step": Bl * Hl * Dl * 2 if world > 1 else 0,
             "shard_imbalance": max(loads) / (sum(loads) / len(loads)),
             "gather_max_abs": probe,
             "gather_check": "rank 0 recomputed one head of its own and one of the last rank's (2 batch rows) from the "
                             "gathered (B, 1, 64, D) with the fp32 CPU oracle; bf16 outputs",
-            "with_o_proj": dict(proj, note="attention + o_proj (8192 x 8192 bf16): gathered form and row-parallel form "
-                                           "(all-reduce of partial products)")}
+            "with_o_proj": dict(proj, note="attention + o_proj (8192 x 8192 bf16): NCCL-gathered form, row-parallel form "
+                                           "(all-reduce of partial products), peer-store gather form")}
 
 
 def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int = 3, batch: int = 32,
@@ -641,12 +670,21 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     for i in range(warmup):
         step(i)
     ms, _ = time_blocks(step, steps, device, dist, min_blocks=3, min_region_s=0.2)
-    per_step = statistics.median(ms) / steps
+    per_step_nccl = per_step = statistics.median(ms) / steps
+    if world > 1:        # the same steps with the gather done by the decode kernel (peer stores + barrier kernel)
+        pg = model.model.enable_peer_gather(batch)
+        for i in range(warmup):
+            step(i)
+        ms, _ = time_blocks(step, steps, device, dist, min_blocks=3, min_region_s=0.2)
+        per_step = statistics.median(ms) / steps
+        pg.check()
+        pg.close()
     weights = sum(prm.numel() for name, prm in model.named_parameters()
                   if prm.dim() > 1 and "embed_tokens" not in name) * 2
     return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
                         f"{layers} layers, heads sharded over {world} GPU(s)",
             "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
+            "ms_per_step_nccl_allgather": per_step_nccl,
             "kv_bytes_per_step_per_gpu": kv_bytes, "weight_bytes_per_step_per_gpu": weights,
             "hbm_gbs_per_gpu": (kv_bytes + weights) / (per_step * 1e-3) / 1e9}
 

@@ -2,7 +2,8 @@
  * moa_b200 — C ABI of the B200 (sm_100a) kernels for MoA's attention hot path.
  *
  * Every entry point takes plain device pointers and sizes, enqueues its work on the CUDA
- * stream it is given, never synchronises the device and never allocates device memory.
+ * stream it is given, never synchronises the device and never allocates device memory
+ * (the moa_peer_alloc / moa_peer_free pair is the one exception, and says so).
  * The return value is a moa_status (0 = MOA_OK); moa_strerror() names it and
  * moa_last_error_detail() gives the CUDA error text of the calling thread's last failure.
  *
@@ -225,6 +226,36 @@ int moa_prefill_fwd(const void* q, const void* k, const void* v, void* out,
 int moa_rope_qk(void* q, void* k, int64_t sb, int64_t sh, int64_t sn, const void* cos, const void* sin,
                 int64_t cos_batch_stride, int64_t cos_token_stride, int B, int H, int64_t N, int D, int dtype,
                 moa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Buffers that the GPUs of one node write into directly (what moa_decode_gather_fwd's out_peers point at),
+ * and a barrier across the ranks.  No counterpart in the reference, which runs on one GPU; together with
+ * moa_decode_gather_fwd they replace the all-gather of the head shards' outputs that has to precede
+ * o_proj (MoA/models/llama/modeling_llama.py:329-330) when heads are sharded over GPUs.
+ *
+ * moa_peer_alloc / moa_peer_free: device memory of the current device that other processes can map
+ *   (cudaMalloc'ed, zero-filled; these two calls allocate and free and synchronise like cudaMalloc/cudaFree:
+ *   set-up time only).
+ * moa_peer_export: writes the MOA_PEER_HANDLE_BYTES-byte handle of such a buffer; send it to the other ranks
+ *   by any host channel.  moa_peer_open maps a handle received from another process of the same node into
+ *   this process (peer access is enabled as needed) and returns the device pointer; moa_peer_close unmaps it.
+ * moa_peer_barrier: enqueues a one-block kernel that (1) publishes `epoch` in word `rank` of every rank's
+ *   flag array and (2) waits until all `world` words of this rank's own array have reached `epoch`.
+ *   flags: host array of `world` device pointers, flags[g] = rank g's array of `world` uint32 words (zero at
+ *   the start; flags[rank] is this rank's own).  Every rank calls it with the same epoch, which must grow by
+ *   one from call to call.  Work enqueued before the barrier on this stream (stores into the peers' buffers)
+ *   is visible to what the other ranks enqueue after theirs.  The wait gives up after limit_cycles SM cycles
+ *   (at most 2e10): status (device int32[4], zero on entry) then holds {21, the rank waited for, epoch, rank}
+ *   and the kernel returns normally.
+ * ------------------------------------------------------------------------------------------ */
+#define MOA_PEER_HANDLE_BYTES 64
+int moa_peer_alloc(void** ptr, int64_t bytes);
+int moa_peer_free(void* ptr);
+int moa_peer_export(void* ptr, void* handle);
+int moa_peer_open(const void* handle, void** ptr);
+int moa_peer_close(void* ptr);
+int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, int64_t limit_cycles, int32_t* status,
+                     moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * moa_selftest_bounded_wait: failure-detection self-test (no counterpart in the reference, which has

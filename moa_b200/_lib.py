@@ -23,7 +23,8 @@ SYMBOLS = (
     "moa_decode_workspace_bytes", "moa_decode_workspace_init", "moa_decode_fwd",
     "moa_cache_append", "moa_cache_scan_mask", "moa_cache_fill", "moa_prefill_fwd",
     "moa_decode_fwd_static", "moa_decode_rope_fwd", "moa_decode_gather_fwd", "moa_selftest_bounded_wait",
-    "moa_rope_qk",
+    "moa_rope_qk", "moa_peer_alloc", "moa_peer_free", "moa_peer_export", "moa_peer_open", "moa_peer_close",
+    "moa_peer_barrier",
 )
 
 
@@ -57,13 +58,20 @@ def _load() -> ctypes.CDLL:
     lib.moa_decode_fwd_static.argtypes = decode_args + [I, P]
     lib.moa_rope_qk.argtypes = [P, P, I64, I64, I64, P, P, I64, I64, I, I, I64, I, I, P]
     lib.moa_selftest_bounded_wait.argtypes = [P, I64, P]
+    lib.moa_peer_alloc.argtypes = [ctypes.POINTER(c_void_p), I64]
+    lib.moa_peer_free.argtypes = [P]
+    lib.moa_peer_export.argtypes = [P, P]
+    lib.moa_peer_open.argtypes = [P, ctypes.POINTER(c_void_p)]
+    lib.moa_peer_close.argtypes = [P]
+    lib.moa_peer_barrier.argtypes = [P, I, I, ctypes.c_uint32, I64, P, P]
     lib.moa_cache_append.argtypes = [P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, I, P]
     lib.moa_cache_scan_mask.argtypes = [P, I64, P, P, I, I64, P]
     lib.moa_cache_fill.argtypes = [P, P, I64, I64, I64, P, P, P, P, P, P, P, P, P, I64, I, I, I64, I, I64, I64, I, P]
     lib.moa_prefill_fwd.argtypes = [P, P, P, P] + [I64] * 12 + [P, P, I, I, I64, I, c_float, I, I, P, P]
     for name in ("moa_decode_workspace_init", "moa_decode_fwd", "moa_decode_rope_fwd", "moa_decode_gather_fwd",
                  "moa_decode_fwd_static", "moa_rope_qk", "moa_selftest_bounded_wait", "moa_cache_append",
-                 "moa_cache_scan_mask", "moa_cache_fill", "moa_prefill_fwd"):
+                 "moa_cache_scan_mask", "moa_cache_fill", "moa_prefill_fwd", "moa_peer_alloc", "moa_peer_free",
+                 "moa_peer_export", "moa_peer_open", "moa_peer_close", "moa_peer_barrier"):
         getattr(lib, name).restype = c_int
     if lib.moa_abi_version() != ABI_VERSION:
         raise ImportError(f"{LIB_PATH}: ABI version {lib.moa_abi_version()} != {ABI_VERSION}; rebuild it "

@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoa_b200.so")
-SOURCES = ["errors.cu", "decode.cu", "cache.cu", "prefill.cu"]
+SOURCES = ["errors.cu", "decode.cu", "cache.cu", "prefill.cu", "peer.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -3,7 +3,10 @@
 Heads are independent in attention and each owns its ring cache, so the path shards by heads with no
 exchange inside attention.  Where a whole layer runs, the per-rank outputs ``(B, q, H/G, D)`` are
 all-gathered into ``(B, q, H, D)`` before ``o_proj`` (NCCL over NVLink; ``gloo`` on CPU in the tests).
-One process per GPU (``torchrun``); nothing here touches peer memory directly.
+One process per GPU (``torchrun``).  ``HeadSharding.all_gather`` is the plain collective; ``PeerGather`` is
+the decode path's fused form: the decode kernel stores its output rows straight into every rank's
+``(B, 1, H, D)`` buffer over NVLink and a barrier kernel orders the stores before the reads, so the step has
+no collective launch and no copy after it.
 
 The step after attention, ``o_proj`` (``MoA/models/llama/modeling_llama.py:329-330`` in the reference),
 comes in two forms here: the gathered one (all-gather the head shards, then the full projection on every
@@ -15,8 +18,9 @@ runs while the first one's shards are in flight.
 """
 from __future__ import annotations
 
+import ctypes
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -150,3 +154,122 @@ class HeadSharding:
         inv = torch.empty(len(self.order), dtype=torch.long, device=gathered.device)
         inv[torch.tensor(self.order, device=gathered.device)] = torch.arange(len(self.order), device=gathered.device)
         return gathered[:, :, inv]
+
+
+class _RawDeviceMemory:
+    """A device pointer presented through ``__cuda_array_interface__`` so that torch can view it (no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class PeerGather:
+    """The gather of the head shards' decode outputs done by the decode kernel itself.
+
+    Every rank owns two ``(B, 1, H, D)`` buffers (used alternately) and a row of flag words in one piece of
+    device memory that the other ranks of the node map into their address space (CUDA IPC).
+    ``decode_and_gather`` runs the fused decode step with ``out`` = this rank's head slice of its own buffer
+    and ``out_peers`` = the same slice of every other rank's buffer (``moa_decode_gather_fwd``: plain stores over
+    NVLink, nothing is loaded from a peer), then a barrier kernel (``moa_peer_barrier``) after which the buffer
+    holds all heads in shard order on every rank.  Two buffers are enough: a rank that is writing buffer
+    ``k`` of call ``c + 2`` has passed the barrier of call ``c + 1``, which every other rank enters only after
+    its ``o_proj`` of call ``c`` has read buffer ``k``.  Calls must be made by all ranks in the same order.
+
+    The barrier's wait is bounded (``wait_seconds``); if a rank never arrives the others carry on with an
+    incomplete buffer and ``check()`` raises.  ``close()`` unmaps and frees; call it on every rank before the
+    process group is destroyed."""
+
+    def __init__(self, sharding: HeadSharding, batch_size: int, head_dim: int, dtype: torch.dtype, device,
+                 wait_seconds: float = 2.0):
+        self.sh = sharding
+        self.B, self.D, self.dtype = batch_size, head_dim, dtype
+        self.device = torch.device(device)
+        G, Hl = sharding.world_size, sharding.heads_per_rank
+        assert 1 <= G <= 8, "PeerGather serves the GPUs of one node (at most 8 ranks)"
+        self.H = G * Hl
+        item = torch.empty((), dtype=dtype).element_size()
+        self.row_bytes = Hl * head_dim * item
+        payload = batch_size * self.H * head_dim * item
+        self.slot_bytes = (payload + 255) // 256 * 256
+        total = 2 * self.slot_bytes + 256
+        lib = _lib.lib
+        with torch.cuda.device(self.device):
+            base = ctypes.c_void_p()
+            _lib.check("moa_peer_alloc", lib.moa_peer_alloc(ctypes.byref(base), total))
+            handle = ctypes.create_string_buffer(64)
+            _lib.check("moa_peer_export", lib.moa_peer_export(base, handle))
+            handles: List[Optional[bytes]] = [None] * G
+            if G > 1:
+                dist.all_gather_object(handles, handle.raw, group=sharding.group)
+            self.bases: List[int] = []
+            for g in range(G):
+                if g == sharding.rank:
+                    self.bases.append(base.value)
+                else:
+                    p = ctypes.c_void_p()
+                    _lib.check("moa_peer_open", lib.moa_peer_open(handles[g], ctypes.byref(p)))
+                    self.bases.append(p.value)
+        self._own = base.value
+        raw = torch.as_tensor(_RawDeviceMemory(base.value, total), device=self.device)
+        self.buffers = [raw[k * self.slot_bytes:k * self.slot_bytes + payload].view(dtype).view(batch_size, 1, self.H, head_dim)
+                        for k in range(2)]
+        self._flag_ptrs = (ctypes.c_void_p * G)(*[b + 2 * self.slot_bytes for b in self.bases])
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.epoch = 0
+        self.limit_cycles = int(min(2e10, max(1.0, wait_seconds) * 2.0e9))
+        if G > 1:
+            dist.barrier(group=sharding.group)       # every rank has mapped every buffer before the first store
+
+    def targets(self) -> Tuple[Tensor, List[int]]:
+        """This call's destination: the local head slice ``(B, 1, H/G, D)`` of the buffer in turn, and the
+        addresses of the same slice in the other ranks' buffers."""
+        k = self.epoch & 1
+        r, Hl = self.sh.rank, self.sh.heads_per_rank
+        off = k * self.slot_bytes + r * self.row_bytes
+        peers = [b + off for g, b in enumerate(self.bases) if g != r]
+        return self.buffers[k][:, :, r * Hl:(r + 1) * Hl], peers
+
+    def barrier(self) -> Tensor:
+        """Orders every rank's stores of this call before the reads that follow on this stream; returns the
+        full ``(B, 1, H, D)`` buffer of the call and moves on to the other buffer."""
+        full = self.buffers[self.epoch & 1]
+        self.epoch += 1
+        with torch.cuda.device(self.device):
+            _lib.check("moa_peer_barrier", _lib.lib.moa_peer_barrier(
+                self._flag_ptrs, self.sh.rank, self.sh.world_size, self.epoch & 0xFFFFFFFF, self.limit_cycles,
+                self.status.data_ptr(), _lib.current_stream(self.device)))
+        return full
+
+    def decode_and_gather(self, cache, query_states: Tensor, key_states: Tensor, value_states: Tensor,
+                          layer_idx: int, sm_scale: float, rope=None) -> Tensor:
+        """``StaticCircularCache.decode_attention`` on this rank's heads with the gather folded in: returns
+        ``(B, 1, H, D)`` with all ranks' heads in shard order."""
+        out, peers = self.targets()
+        with _lib.nvtx_range("moa_b200.decode_and_gather"):
+            cache.decode_attention(query_states, key_states, value_states, layer_idx, sm_scale, out=out, rope=rope,
+                                   out_peers=peers)
+            return self.barrier()
+
+    def check(self) -> None:
+        """Synchronises and raises if a barrier gave up waiting for a rank."""
+        torch.cuda.synchronize(self.device)
+        words = self.status.tolist()
+        if words[0] != 0:
+            self.status.zero_()
+            raise _lib.MoaError("moa_peer_barrier", 5, _lib.lib.moa_strerror(5).decode(),
+                                f"rank {words[3]} gave up waiting for rank {words[1]} at call {words[2]}")
+
+    def close(self) -> None:
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.sh.world_size > 1:
+            dist.barrier(group=self.sh.group)        # nobody is still storing into a buffer that goes away
+        with torch.cuda.device(self.device):
+            for g, b in enumerate(self.bases):
+                if g != self.sh.rank:
+                    _lib.lib.moa_peer_close(b)
+            self.buffers = []
+            _lib.lib.moa_peer_free(self._own)
+        self._own = None

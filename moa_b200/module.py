@@ -93,6 +93,7 @@ class MoAAttention(nn.Module):
         self.v_proj = nn.Linear(hidden_size, self.num_local_heads * self.head_dim, **kw)
         self.o_proj = nn.Linear(num_heads * self.head_dim, hidden_size, **kw)
         self.gather: Optional[Callable[[Tensor], Tensor]] = None
+        self.peer_gather = None     # a dist.PeerGather: decode steps then deliver their rows to every rank themselves
         self._qkv: Optional[Tensor] = None
 
     def fused_qkv_weight(self) -> Tensor:
@@ -125,6 +126,9 @@ class MoAAttention(nn.Module):
         sm_scale = D ** -0.5
         if q_len == 1:
             # one launch: rotary embedding of q and k, ring append, flash-decoding, bookkeeping
+            if self.peer_gather is not None:    # ... and delivery of the rows to every rank: (B, 1, H, D) comes back
+                return self.peer_gather.decode_and_gather(past_key_value, q, k, v, self.layer_idx, sm_scale,
+                                                          rope=(cos, sin))
             return past_key_value.decode_attention(q, k, v, self.layer_idx, sm_scale, out=out, rope=(cos, sin))
         q, k = apply_rotary_pos_emb(q, k, cos, sin)
         past_key_value.update(k, v, self.layer_idx)
@@ -150,7 +154,7 @@ class MoAAttention(nn.Module):
             assert position_ids is not None, "position_ids or position_embeddings are required"
             position_embeddings = rotary_cos_sin(position_ids, self.head_dim, self.rope_theta, hidden_states.dtype)
         attn = self.attend(hidden_states, past_key_value, position_embeddings)
-        if self.gather is not None:
+        if self.gather is not None and attn.shape[2] != self.num_heads:
             attn = self.gather(attn)
         attn = attn.reshape(bsz, q_len, self.num_heads * self.head_dim)
         return self.o_proj(attn), None, past_key_value
@@ -295,6 +299,20 @@ class MoALlamaModel(nn.Module):
             shardings.append(sh)
         self.head_shardings = shardings
         self.local_moa_config = local
+
+    def enable_peer_gather(self, batch_size: int, wait_seconds: float = 2.0):
+        """Decode steps of a head-sharded model deliver their output rows to every rank's gather buffer from
+        inside the decode kernel (``dist.PeerGather``) instead of through an all-gather collective.  One set
+        of buffers serves all layers.  Collective call (all ranks, after ``shard_heads``); returns the
+        ``PeerGather`` (``check()`` reports a rank that went missing, ``close()`` releases the buffers)."""
+        from .dist import PeerGather
+
+        assert self.head_shardings is not None, "shard the heads first"
+        pg = PeerGather(self.head_shardings[0], batch_size, self.hidden_size // self.num_heads, self.dtype,
+                        self.device, wait_seconds)
+        for layer in self.layers:
+            layer.self_attn.peer_gather = pg
+        return pg
 
     def new_cache(self, batch_size: int, seq_length: int) -> StaticCircularCache:
         """The cache the reference builds on the first forward (modeling_llama.py:93-112); with sharded heads,

@@ -58,6 +58,56 @@ def _worker(rank, world, port, ret):
             scale = float(y_ref.abs().max())
             worst = max(worst, float((y_g.float() - y_ref).abs().max()) / scale * 0.25,
                         float((y_r.float() - y_ref).abs().max()) / scale * 0.25)   # fp16 GEMM: 4e-3 relative
+        # the fused form: the decode kernel stores its rows into every rank's gather buffer, a barrier kernel
+        # orders them; same result as the collective, bit for bit, call after call (two buffers alternate)
+        local2 = moa_b200.StaticCircularCache([sh.slice_plan(caps)], B, D, [[64] * len(mine)], dev, torch.float16)
+        local2.update(k[:, mine], v[:, mine], 0)
+        local3 = moa_b200.StaticCircularCache([sh.slice_plan(caps)], B, D, [[64] * len(mine)], dev, torch.float16)
+        local3.update(k[:, mine], v[:, mine], 0)
+        pg = moa_b200.PeerGather(sh, B, D, torch.float16, dev)
+        for _ in range(5):
+            q, k1, v1 = (torch.randn(B, H, 1, D, generator=gen).half().to(dev) for _ in range(3))
+            args = (q[:, mine].contiguous(), k1[:, mine].contiguous(), v1[:, mine].contiguous(), 0, D ** -0.5)
+            want = sh.all_gather(local2.decode_attention(*args)).clone()
+            got = pg.decode_and_gather(local3, *args)
+            assert torch.equal(got, want)
+        pg.check()
+        pg.close()
+
+        # model level: head-sharded model (collective gather, then the fused gather) against the unsharded model
+        plan = {"alphas": [[1024.0, 128.0, 512.0, 128.0], [256.0, 256.0, 64.0, 2048.0]],
+                "betas": [[0.0, 0.25, 0.0, 0.5], [0.125, 0.0, 0.5, 0.0]]}
+
+        def tiny():
+            torch.manual_seed(5)
+            m = moa_b200.MoALlamaForCausalLM(2, 512, 4, 1024, vocab_size=100, dtype=torch.float16, device=dev)
+            for p in m.parameters():
+                if p.dim() > 1:
+                    p.data.normal_(0, 0.03)
+            m.set_mixture_of_attention(plan, moa_max_new_token=64)
+            return m
+
+        gen2 = torch.Generator().manual_seed(9)
+        ids = torch.randint(0, 100, (2, 300), generator=gen2).to(dev)
+        nxt = [torch.randint(0, 100, (2, 1), generator=gen2).to(dev) for _ in range(4)]
+        ref_m, sh_m = tiny(), tiny()
+        sh_m.model.shard_heads(world, rank, seq_len=300)
+        for h in sh_m.model.head_shardings:
+            h.verify_consistent()
+        a, ca = ref_m(ids)
+        b, cb = sh_m(ids)
+        rel = lambda x, y: float((x.float() - y.float()).abs().mean() / y.float().abs().mean())
+        worst_model = rel(b, a)
+        pg = None
+        for i, t in enumerate(nxt):
+            if i == 2:                      # from here on the decode kernel does the gather itself
+                pg = sh_m.model.enable_peer_gather(2)
+            a, ca = ref_m(t, past_key_values=ca)
+            b, cb = sh_m(t, past_key_values=cb)
+            worst_model = max(worst_model, rel(b, a))
+        pg.check()
+        pg.close()
+        assert worst_model < 1e-2, worst_model
         ret[rank] = worst
     finally:
         dist.destroy_process_group()
@@ -99,3 +149,28 @@ def test_one_process_driving_two_gpus():
         assert (out.float().cpu() - ref).abs().max() <= 2e-3, dev
         got = moa_b200.sparse_decode(qd.to(dev), kc.to(dev), vc.to(dev), starts.to(dev), valid.to(dev), 0.1)
         assert (got.float().cpu() - dref).abs().max() <= 2e-3, dev
+
+
+def test_peer_barrier_gives_up_when_a_rank_never_arrives():
+    """Failure detection without a fault: rank 0 of a pretended two-rank group runs the barrier, the flag word
+    the absent rank would set stays zero, the bounded wait runs out, the status words say who was missing, and
+    the context stays usable (one GPU, no peer)."""
+    import ctypes
+    from moa_b200 import _lib
+    lib = _lib.lib
+    flags0 = torch.zeros(8, dtype=torch.int32, device="cuda")      # rank 0's flag words
+    flags1 = torch.zeros(8, dtype=torch.int32, device="cuda")      # stands for the absent rank's (nobody reads them)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(flags0.data_ptr(), flags1.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.moa_peer_barrier(ptrs, 0, 2, 1, 20_000_000, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert status.tolist() == [21, 1, 1, 0]
+    assert flags0.tolist()[:2] == [1, 0] and flags1.tolist()[0] == 1      # rank 0 published its arrival to both
+    # a barrier whose partner has arrived (the word is already there) passes and leaves the status alone
+    status.zero_()
+    flags0[1] = 2
+    assert lib.moa_peer_barrier(ptrs, 0, 2, 2, 20_000_000, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert lib.moa_peer_barrier(ptrs, 0, 9, 3, 1000, status.data_ptr(), stream) == 1       # more than 8 ranks: refused
