@@ -198,12 +198,15 @@ int moa_cache_fill(const void* k, const void* v, int64_t sb, int64_t sh, int64_t
  *            every stride a multiple of 8 elements, base pointers 16-byte aligned
  *   out      written as out[b*ob + n*on + h*oh + d]; (B,N,H,D) contiguous is ob=N*H*D, on=H*D, oh=D
  *   sink_blocks, local_blocks (H) int32 device arrays, in 64-token blocks
- *   status   device int32[4], zero on entry; a non-zero word after the kernel finished means a
- *            bounded wait inside the kernel gave up (MOA_ERR_DEVICE_WAIT) and out is invalid.
+ *   status   device int32[8], zero on entry, owned by this launch until it has finished (launches that can
+ *            overlap in time need a buffer each).  Words 0-3 report a bounded wait that gave up: a non-zero
+ *            word 0 after the kernel finished means MOA_ERR_DEVICE_WAIT and out is invalid.
  *            status[0] = what was waited for (1 Q tiles, 2 a K tile, 3 a free K stage, 4 S from the
  *            tensor core, 5 P from the softmax warps, 6 the last but one P.V, 7 the final O, 8 a V
- *            tile, 9 a free V stage, 11 the issuer's turn on the tensor core); status[1] = blockIdx.x,
- *            status[2] = blockIdx.y + 65536 * blockIdx.z, status[3] = threadIdx.x of the waiter
+ *            tile, 9 a free V stage, 11 the issuer's turn on the tensor core, 12 the next unit of work,
+ *            13 a free slot to publish it in, 14 the Q tiles to be free); status[1] = blockIdx.x,
+ *            status[2] = 0, status[3] = threadIdx.x of the waiter.  Words 4-5 are the work scheduler's
+ *            (next query tile to hand out, blocks finished); the kernel leaves them zero again.
  *   out_f32 non-zero: out is float32 (same math, fp32 store) — used to check the bf16 path
  * ------------------------------------------------------------------------------------------ */
 int moa_prefill_fwd(const void* q, const void* k, const void* v, void* out,

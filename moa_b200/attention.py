@@ -28,13 +28,16 @@ _status: Dict = {}
 # what the waiting thread was waiting for (the codes the prefill kernel writes to its status words)
 _WAIT_NAMES = {1: "Q tiles", 2: "a K tile", 3: "a free K stage", 4: "S from the tensor core", 5: "P from the softmax warps",
                6: "the last but one P.V", 7: "the final O", 8: "a V tile", 9: "a free V stage",
-               11: "its turn on the tensor core"}
+               11: "its turn on the tensor core", 12: "the next unit of work", 13: "a free slot for the next unit",
+               14: "the Q tiles to be free"}
 
 
 def _status_words(device) -> Tensor:
-    key = torch.device(device)
+    """The int32[8] status buffer of the prefill kernel (wait report + its scheduler words), one per device and
+    stream: launches on different streams may overlap and must not share one."""
+    key = (torch.device(device), torch.cuda.current_stream(device).cuda_stream)
     if key not in _status:
-        _status[key] = torch.zeros(4, dtype=torch.int32, device=key)
+        _status[key] = torch.zeros(8, dtype=torch.int32, device=key[0])
     return _status[key]
 
 
@@ -42,17 +45,19 @@ def check_device_status(device=None) -> None:
     """Synchronise and raise if a kernel on ``device`` reported that one of its bounded waits ran
     out (its output is then invalid).  Cheap enough for tests and once-per-request checks; the
     hot path never synchronises."""
-    devices = [torch.device(device)] if device is not None else list(_status.keys())
-    for dev in devices:
-        if dev in _status:
-            torch.cuda.synchronize(dev)
-            words = _status[dev].tolist()
-            if words[0] != 0:
-                _status[dev].zero_()
-                what = _WAIT_NAMES.get(words[0], "?")
-                raise _lib.MoaError("moa_prefill_fwd", 5, lib.moa_strerror(5).decode(),
-                                    f"wait code {words[0]} ({what}) in block x={words[1]} yz={words[2]} "
-                                    f"thread {words[3]}")
+    want = torch.device(device) if device is not None else None
+    if want is not None and want.index is None and want.type == "cuda":
+        want = torch.device("cuda", torch.cuda.current_device())
+    for (dev, _stream), buf in list(_status.items()):
+        if want is not None and dev != want:
+            continue
+        torch.cuda.synchronize(dev)
+        words = buf.tolist()
+        if words[0] != 0:
+            buf.zero_()
+            what = _WAIT_NAMES.get(words[0], "?")
+            raise _lib.MoaError("moa_prefill_fwd", 5, lib.moa_strerror(5).decode(),
+                                f"wait code {words[0]} ({what}) in block {words[1]} thread {words[3]}")
 
 
 def _decode_workspace(device, B: int, H: int, D: int, S: int) -> Tensor:

@@ -1,14 +1,17 @@
 // Block-sparse causal prefill (attention sink + per-head sliding window) on tcgen05 / TMEM / TMA.
 //
-// One thread block computes a 256-row query super-tile of one (batch, head) as two 128-row tiles
-// A and B that share every K/V tile brought into shared memory.  Roles:
+// A persistent kernel: one thread block per SM, each working through 256-row query super-tiles of one
+// (batch, head) handed out by an atomic counter, heaviest first.  A super-tile is two 128-row tiles A and B
+// that share every K/V tile brought into shared memory.  Roles:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
 //              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM, computes the
 //              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
 //              column) over the first half of the S buffer the row came from, rescales O in TMEM
 //              when the max moved, and finally runs the epilogue
-//   warp  8    TMA producer (one lane): both Q tiles once, then K and V tiles of 64 tokens through
-//              two rings of shared-memory stages
+//   warp  8    scheduler + TMA producer (one lane): fetches the next super-tile, publishes it to the other
+//              roles through a two-entry ring, loads both Q tiles, then K and V tiles of 64 tokens through
+//              two rings of shared-memory stages.  It runs ahead of the others: the next super-tile's Q and
+//              first K/V tiles arrive while the softmax warps are still in the epilogue of this one
 //   warp  9,10 MMA issuers of tile A and tile B (warp 9 owns the TMEM allocation):
 //              S = Q K^T (M128 N64 K128, Q and K from shared memory), O += P V (M128 N128 K64,
 //              P from TMEM, V from shared memory as an MN-major operand).  The whole warp runs the
@@ -18,10 +21,15 @@
 // Each tile has two S/P buffers in TMEM.  On the tensor core its order is S(0), S(1), then per step
 // i: [softmax turns S(i) into P(i)] -> O += P(i) V(i) -> S(i+2), the last one into the buffer P(i)
 // was read from: MMAs of one issuing thread execute in order, so no barrier guards the buffers,
-// and S runs a whole step ahead of the exponentials.  Shared-memory stages go back to the producer
-// through tcgen05.commit.  Only the 64-token KV blocks inside "sink U band" of the super-tile are
-// loaded; a tile skips the blocks only the other tile sees, and only the (at most three) edge
-// blocks of a tile get an element mask.
+// and S runs a whole step ahead of the exponentials.  The same order carries over from one super-tile to
+// the next: its S(0) and S(1) are issued right behind the last O += P V, and the first O += P V of the
+// next super-tile (which overwrites O) waits for a P that the softmax threads only produce after their
+// epilogue has read O.  Shared-memory stages go back to the producer through tcgen05.commit.  Only the
+// 64-token KV blocks inside "sink U band" of the super-tile are loaded; a tile skips the blocks only the
+// other tile sees, and only the (at most three) edge blocks of a tile get an element mask.
+//
+// Every mbarrier is used with a running count kept by each role (stage or buffer = count mod ring size,
+// parity = the next bit), so phases carry over from super-tile to super-tile.
 //
 // The mask (MoA/kernels/block_sparse_attention_prefill.py:558-580): query block bi = row/64 sees
 // KV block j iff j <= bi and (j < sink_blocks[h] or j >= bi + 1 - local_blocks[h]); inside a
@@ -65,10 +73,13 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;      // same bound for the drai
 
 // status codes written to status[0] when a wait gives up
 enum { kWaitQ = 1, kWaitKFull = 2, kWaitKEmpty = 3, kWaitS = 4, kWaitP = 5, kWaitPV = 6, kWaitO = 7,
-       kWaitVFull = 8, kWaitVEmpty = 9, kWaitLock = 11 };
+       kWaitVFull = 8, kWaitVEmpty = 9, kWaitLock = 11, kWaitTile = 12, kWaitTileSlot = 13, kWaitQEmpty = 14 };
 
 struct Ctl {
-  uint64_t q_full;
+  uint64_t q_full;               // producer -> issuers: both Q tiles of the super-tile are in shared memory
+  uint64_t q_empty[2];           // [tile] issuer -> producer: that tile's Q K^T of the super-tile have all been executed
+                                 // (one barrier per issuer: an issuer with nothing to do in the next super-tile arrives
+                                 // again at once, and must not be taken for the other one)
   uint64_t k_full[kStages];
   uint64_t v_full[kStages];
   uint64_t k_empty[2][kStages];  // [tile]: that tile is done with the K stage
@@ -79,11 +90,15 @@ struct Ctl {
                           // then have advanced two phases, which a parity wait cannot tell from none
   uint64_t pv_done[2];  // [tile] tensor core -> softmax: the last but one O += P V has finished (O may be rescaled)
   uint64_t o_full[2];
+  uint64_t tile_full[2];   // producer -> everyone: tile_id[slot] holds the next super-tile (or -1: no more)
+  uint64_t tile_empty[2];  // everyone -> producer: the slot has been read (count kTileReaders)
+  int tile_id[2];
   uint32_t tmem_base;
   int abort;
   int pipe_lock;   // held by the issuer whose batch of MMAs is being queued
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
+constexpr int kTileReaders = 2 + 8;   // one elected lane of each issuer warp, lane 0 of each softmax warp
 
 struct PrefillParams {
   void* out;
@@ -93,8 +108,10 @@ struct PrefillParams {
   int B, H;
   int64_t N;
   float scale_log2;
-  int heads_fastest;
-  int32_t* status;
+  int chunk;         // consecutive super-tiles of a head that are handed out together (see tile_coord)
+  int nsuper;        // 256-row super-tiles per (batch, head)
+  int num_tiles;     // B * H * nsuper
+  int32_t* status;   // [0..3] wait report; [4] next super-tile to hand out, [5] blocks that have finished
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -317,9 +334,74 @@ __device__ __forceinline__ TileSeen tile_seen(bool exists, int t, const TileBloc
   return r;
 }
 
+// Which (batch, head, super-tile) the n-th handed-out unit is.  A head's super-tiles get heavier towards the end
+// of the sequence (until the window is full), so units are handed out from the end of the sequence backwards,
+// in chunks of `chunk` consecutive super-tiles per head: chunk by chunk, inside a chunk head by head, inside a
+// head from the last super-tile down.  Every head's heavy tiles therefore start early and the launch ends on
+// cheap ones (the longest-processing-time order, up to the chunk), while the blocks working at the same time
+// still hold neighbouring super-tiles of a head, which share their K/V band in L2.  chunk = 1 interleaves the
+// heads completely; chunk = nsuper takes one head after the other.
+struct TileCoord {
+  int b, h, st;
+};
+__device__ __forceinline__ TileCoord tile_coord(int unit, const PrefillParams& p) {
+  const int heads = p.B * p.H;
+  const int per_chunk = heads * p.chunk;              // units in a full chunk
+  const int full = p.nsuper / p.chunk;                // full chunks, counted from the end of the sequence
+  int k = unit / per_chunk, width = p.chunk, r = unit - k * per_chunk;
+  if (k >= full) {                                    // the partial chunk at the start of the sequence
+    k = full;
+    width = p.nsuper - full * p.chunk;
+    r = unit - full * per_chunk;
+  }
+  const int bh = r / width, j = r - bh * width;
+  TileCoord c;
+  c.b = bh / p.H;
+  c.h = bh - c.b * p.H;
+  c.st = p.nsuper - 1 - k * p.chunk - j;
+  return c;
+}
+
+// Everything a role derives from a super-tile's coordinates.
+struct TileWork {
+  int b, h, t0, nb, sink_b, local_b, nkv;
+  bool active1;       // the second 128-row tile exists
+  TileBlocks tb;
+};
+// WARP: called by a whole converged warp.  The unit and the two values loaded from the plan are then passed
+// through a lane-0 broadcast, which lets the compiler see that everything derived from them is the same in
+// all lanes and keep it in uniform registers — what the MMA issuers' descriptors and addresses need (values
+// read from shared or global memory are not known to be uniform otherwise, and the issue path gets slower).
+template <bool WARP>
+__device__ __forceinline__ TileWork tile_work(int unit, const PrefillParams& p) {
+  if (WARP) unit = __shfl_sync(0xffffffffu, unit, 0);
+  const TileCoord c = tile_coord(unit, p);
+  TileWork w;
+  w.b = c.b;
+  w.h = c.h;
+  w.t0 = 2 * c.st;
+  w.nb = (int)((p.N + kBN - 1) / kBN);
+  w.sink_b = p.sink_blocks[c.h];
+  w.local_b = p.local_blocks[c.h];
+  if (WARP) {
+    w.sink_b = __shfl_sync(0xffffffffu, w.sink_b, 0);
+    w.local_b = __shfl_sync(0xffffffffu, w.local_b, 0);
+  }
+  w.active1 = (int64_t)(w.t0 + 1) * kBM < p.N;
+  w.tb = tile_blocks(w.t0, w.active1 ? w.t0 + 1 : w.t0, w.nb, w.sink_b, w.local_b);
+  w.nkv = w.tb.count();
+  return w;
+}
+
 // DH = head_dim, 64 or 128.  The shared-memory and TMEM layout is the one of 128; with 64 only the first
 // 64-column panel of every Q/K/V tile and the first 64 O columns are used.
-template <typename T, bool OUT_F32, int DH>
+//
+// PERSISTENT: the block keeps taking units from the counter until there are none left (the grid is one block per
+// SM).  Otherwise the block computes the one unit that is its index (the grid is one block per unit, handed to
+// the SMs in order by the hardware) and the loops below run once: the form for long sequences, where a
+// super-tile runs for hundreds of steps, the hand-over between units does not matter, and the code the compiler
+// makes of the single pass is a few per cent faster per step.
+template <typename T, bool OUT_F32, int DH, bool PERSISTENT>
 __global__ void __launch_bounds__(kThreads, 1)
 moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
@@ -328,26 +410,22 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemCtl);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nsuper = (int)((p.N + 2 * kBM - 1) / (2 * kBM));
-  // Blocks are dispatched with x fastest, heaviest super-tiles first.  Long sequences put the tiles
-  // of one head next to each other (neighbours share their K/V band in L2); short ones put the heads
-  // next to each other so that every head's heavy tiles start early.
-  const int b = blockIdx.z;
-  const int h = p.heads_fastest ? blockIdx.x : blockIdx.y;
-  const int st = nsuper - 1 - (int)(p.heads_fastest ? blockIdx.y : blockIdx.x);
-  const int nb = (int)((p.N + kBN - 1) / kBN);
-  const int sink_b = p.sink_blocks[h], local_b = p.local_blocks[h];
-  const int t0 = 2 * st, t1 = 2 * st + 1;
-  const bool active1 = (int64_t)t1 * kBM < p.N;      // the second tile exists
-  const TileBlocks tb = tile_blocks(t0, active1 ? t1 : t0, nb, sink_b, local_b);
-  const int nkv = tb.count();
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr int NH = DH / 64;                 // 64-column panels per tile
   constexpr int kQPanel = kBM * 128, kKPanel = kBN * 128;   // bytes of one panel
   static_assert(DH == 64 || DH == 128, "head_dim");
 
+  // the block's first unit is its own index: fetch its head's plan while the barriers and TMEM are set up
+  const TileWork w_first = tile_work<true>((int)blockIdx.x, p);
+  if (warp == 8 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
+    mbar_init(&ctl->q_empty[0], 1);
+    mbar_init(&ctl->q_empty[1], 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl->k_full[s], 1);
       mbar_init(&ctl->v_full[s], 1);
@@ -363,6 +441,8 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&ctl->p_full[x][1], kSoftmaxThreads);
       mbar_init(&ctl->pv_done[x], 1);
       mbar_init(&ctl->o_full[x], 1);
+      mbar_init(&ctl->tile_full[x], 1);
+      mbar_init(&ctl->tile_empty[x], kTileReaders);
     }
     ctl->abort = 0;
     ctl->pipe_lock = 0;
@@ -380,60 +460,100 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t tmem = *(volatile uint32_t*)&ctl->tmem_base;
 
   if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
-      mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
-#pragma unroll
-      for (int hf = 0; hf < NH; ++hf) {
-        tma_load_4d(smem + kSmemQ + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, t0 * kBM, h, b);
-        tma_load_4d(smem + kSmemQ + kQBytes + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, t1 * kBM, h, b);
-      }
-      int k_issued = 0, v_issued = 0;
+      uint32_t ring = 0;            // K (and V) ring entries of the super-tiles before this one
+      uint32_t k_issued = 0, v_issued = 0, q_issued = 0;
       bool ok = true;
-      // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
-      // tiles' issuers have handed it back.
-      for (int u = 0; ok && u <= nkv; ++u) {
-        if (u < nkv) {
-          const int s = u & (kStages - 1);
-          const uint32_t par = ((u / kStages) & 1) ^ 1;
-          ok = mbar_wait(&ctl->k_empty[0][s], par, ctl, p.status, kWaitKEmpty) &&
-               mbar_wait(&ctl->k_empty[1][s], par, ctl, p.status, kWaitKEmpty);
+      for (uint32_t n = 0; ok; ++n) {
+        int unit = (int)blockIdx.x;      // the first unit of a block is its own index
+        if (PERSISTENT) {
+          if (n > 0) unit = (int)gridDim.x + atomicAdd(&p.status[4], 1);   // later ones come from the counter
+          if (unit >= p.num_tiles) unit = -1;
+          const int slot = n & 1;
+          // Q may be overwritten once both issuers' Q K^T of the previous super-tile have been executed.  This
+          // wait comes before the next unit is published: an issuer with nothing to do in it hands Q back at
+          // once, and that second arrival must not land before the first one has been seen here.
+          if (n > 0) {
+            ok = mbar_wait(&ctl->q_empty[0], (n - 1) & 1, ctl, p.status, kWaitQEmpty) &&
+                 mbar_wait(&ctl->q_empty[1], (n - 1) & 1, ctl, p.status, kWaitQEmpty);
+            if (!ok) break;
+          }
+          ok = mbar_wait(&ctl->tile_empty[slot], ((n >> 1) & 1) ^ 1, ctl, p.status, kWaitTileSlot);
           if (!ok) break;
-          uint8_t* dst = smem + kSmemK + s * kKBytes;
-          const int row = tb.block(u) * kBN;
-          mbar_expect_tx(&ctl->k_full[s], NH * kKPanel);
-#pragma unroll
-          for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_k, &ctl->k_full[s], 64 * hf, row, h, b);
-          k_issued = u + 1;
+          *(volatile int*)&ctl->tile_id[slot] = unit;
+          mbar_arrive(&ctl->tile_full[slot]);
+          if (unit < 0) break;
+        } else if (n > 0) {
+          break;
         }
-        if (u >= 1) {
-          const int uv = u - 1, s = uv & (kStages - 1);
-          const uint32_t par = ((uv / kStages) & 1) ^ 1;
-          ok = mbar_wait(&ctl->v_empty[0][s], par, ctl, p.status, kWaitVEmpty) &&
-               mbar_wait(&ctl->v_empty[1][s], par, ctl, p.status, kWaitVEmpty);
-          if (!ok) break;
-          uint8_t* dst = smem + kSmemV + s * kKBytes;
-          const int row = tb.block(uv) * kBN;
-          mbar_expect_tx(&ctl->v_full[s], NH * kKPanel);
+        const TileWork w = (n == 0) ? w_first : tile_work<false>(unit, p);
+        mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
 #pragma unroll
-          for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_v, &ctl->v_full[s], 64 * hf, row, h, b);
-          v_issued = uv + 1;
+        for (int hf = 0; hf < NH; ++hf) {
+          tma_load_4d(smem + kSmemQ + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, w.t0 * kBM, w.h, w.b);
+          tma_load_4d(smem + kSmemQ + kQBytes + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, (w.t0 + 1) * kBM, w.h, w.b);
+        }
+        q_issued = n + 1;
+        // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
+        // tiles' issuers have handed it back.
+        for (int u = 0; ok && u <= w.nkv; ++u) {
+          if (u < w.nkv) {
+            const uint32_t g = ring + u;
+            const int s = g & (kStages - 1);
+            const uint32_t par = ((g / kStages) & 1) ^ 1;
+            ok = mbar_wait(&ctl->k_empty[0][s], par, ctl, p.status, kWaitKEmpty) &&
+                 mbar_wait(&ctl->k_empty[1][s], par, ctl, p.status, kWaitKEmpty);
+            if (!ok) break;
+            uint8_t* dst = smem + kSmemK + s * kKBytes;
+            const int row = w.tb.block(u) * kBN;
+            mbar_expect_tx(&ctl->k_full[s], NH * kKPanel);
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_k, &ctl->k_full[s], 64 * hf, row, w.h, w.b);
+            k_issued = g + 1;
+          }
+          if (u >= 1) {
+            const uint32_t g = ring + u - 1;
+            const int s = g & (kStages - 1);
+            const uint32_t par = ((g / kStages) & 1) ^ 1;
+            ok = mbar_wait(&ctl->v_empty[0][s], par, ctl, p.status, kWaitVEmpty) &&
+                 mbar_wait(&ctl->v_empty[1][s], par, ctl, p.status, kWaitVEmpty);
+            if (!ok) break;
+            uint8_t* dst = smem + kSmemV + s * kKBytes;
+            const int row = w.tb.block(u - 1) * kBN;
+            mbar_expect_tx(&ctl->v_full[s], NH * kKPanel);
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) tma_load_4d(dst + hf * kKPanel, &map_v, &ctl->v_full[s], 64 * hf, row, w.h, w.b);
+            v_issued = g + 1;
+          }
+        }
+        ring += (uint32_t)w.nkv;
+      }
+      // This block has taken its last unit (or is giving up).  The last block to get here puts the scheduler
+      // words back to zero for the next launch — nobody touches them any more — while the others still compute.
+      if (PERSISTENT) {
+        __threadfence();
+        if (atomicAdd(&p.status[5], 1) == (int)gridDim.x - 1) {
+          p.status[4] = 0;
+          p.status[5] = 0;
         }
       }
       if (*(volatile int*)&ctl->abort) {
         // drain: shared memory must not be released while bulk copies into it are in flight
         const uint64_t tstart = globaltimer_ns();
-        for (int u = max(0, k_issued - kStages); u < k_issued; ++u) {
-          while (!mbar_try_wait(&ctl->k_full[u & (kStages - 1)], (u / kStages) & 1) &&
+        for (uint32_t g = k_issued > (uint32_t)kStages ? k_issued - kStages : 0; g < k_issued; ++g) {
+          while (!mbar_try_wait(&ctl->k_full[g & (kStages - 1)], (g / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        for (int u = max(0, v_issued - kStages); u < v_issued; ++u) {
-          while (!mbar_try_wait(&ctl->v_full[u & (kStages - 1)], (u / kStages) & 1) &&
+        for (uint32_t g = v_issued > (uint32_t)kStages ? v_issued - kStages : 0; g < v_issued; ++g) {
+          while (!mbar_try_wait(&ctl->v_full[g & (kStages - 1)], (g / kStages) & 1) &&
                  globaltimer_ns() - tstart < kWaitLimitNs) {
           }
         }
-        while (!mbar_try_wait(&ctl->q_full, 0) && globaltimer_ns() - tstart < kWaitLimitNs) {
+        if (q_issued > 0) {
+          while (!mbar_try_wait(&ctl->q_full, (q_issued - 1) & 1) && globaltimer_ns() - tstart < kWaitLimitNs) {
+          }
         }
       }
     }
@@ -446,81 +566,106 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // Order on the tensor core for this tile: S(0), S(1), then for every step i: O += P(i) V(i), S(i+2).
     // S(i+2) goes into the buffer P(i) is read from; MMAs of one thread execute in order, so it cannot
     // overtake that read, and no barrier is needed for the buffer.
-    {
-      const int x = warp - 9;
-      const TileSeen seen = tile_seen(x == 0 || active1, t0 + x, tb, nb, local_b);
-      constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
-      constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, DH);
-      // descriptors differ only in their start-address field (bytes >> 4): build each base once
-      const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
-      const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
-      const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
-      const uint32_t o_tmem = tmem + col_o(x);
-      uint64_t* const k_empty = ctl->k_empty[x];
-      uint64_t* const v_empty = ctl->v_empty[x];
-      bool ok = true;
-      auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
-        const bool mine = mbar_wait(bar, parity, ctl, p.status, code);
-        ok = __all_sync(0xffffffffu, mine);
-      };
+    const int x = warp - 9;
+    constexpr uint32_t idesc_qk = make_idesc(kBf16, 0, kBM, kBN);
+    constexpr uint32_t idesc_pv = make_idesc(kBf16, 1, kBM, DH);
+    // descriptors differ only in their start-address field (bytes >> 4): build each base once
+    const uint64_t q_desc = make_desc(smem_u32(smem + kSmemQ + x * kQBytes), 16, 1024);
+    const uint64_t k_desc0 = make_desc(smem_u32(smem + kSmemK), 16, 1024);
+    const uint64_t v_desc0 = make_desc(smem_u32(smem + kSmemV), kKBytes / 2, 1024);
+    const uint32_t o_tmem = tmem + col_o(x);
+    uint64_t* const k_empty = ctl->k_empty[x];
+    uint64_t* const v_empty = ctl->v_empty[x];
+    uint32_t ring = 0;   // K/V ring entries of the super-tiles before this one
+    uint32_t sbase = 0;  // S/P buffers this tile has used before this super-tile
+    bool ok = true;
+    auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+      const bool mine = mbar_wait(bar, parity, ctl, p.status, code);
+      ok = __all_sync(0xffffffffu, mine);
+    };
+
+    for (uint32_t n = 0; ok; ++n) {
+      int unit = (int)blockIdx.x;
+      if (PERSISTENT) {
+        const int slot = n & 1;
+        wait(&ctl->tile_full[slot], (n >> 1) & 1, kWaitTile);
+        if (!ok) break;
+        unit = *(volatile int*)&ctl->tile_id[slot];
+        __syncwarp();
+        if (elect_one()) mbar_arrive(&ctl->tile_empty[slot]);
+        if (unit < 0) break;
+      } else if (n > 0) {
+        break;
+      }
+      const TileWork w = (n == 0) ? w_first : tile_work<true>(unit, p);
+      const int nkv = w.nkv;
+      const TileSeen seen = tile_seen(x == 0 || w.active1, w.t0 + x, w.tb, w.nb, w.local_b);
 
       // Hand back ring entries [from, to) this tile does not use (rare: at most a few per tile).  The stage
       // must have been filled first, so that the arrives of successive ring rounds cannot run ahead of the
       // producer.
       auto skip_k = [&](int from, int to) {
-        for (int w = from; ok && w < to; ++w) {
-          const int s = w & (kStages - 1);
-          wait(&ctl->k_full[s], (w / kStages) & 1, kWaitKFull);
+        for (int e = from; ok && e < to; ++e) {
+          const uint32_t g = ring + e;
+          const int s = g & (kStages - 1);
+          wait(&ctl->k_full[s], (g / kStages) & 1, kWaitKFull);
           if (ok && elect_one()) mbar_arrive(&k_empty[s]);
         }
       };
       auto skip_v = [&](int from, int to) {
-        for (int w = from; ok && w < to; ++w) {
-          const int s = w & (kStages - 1);
-          wait(&ctl->v_full[s], (w / kStages) & 1, kWaitVFull);
+        for (int e = from; ok && e < to; ++e) {
+          const uint32_t g = ring + e;
+          const int s = g & (kStages - 1);
+          wait(&ctl->v_full[s], (g / kStages) & 1, kWaitVFull);
           if (ok && elect_one()) mbar_arrive(&v_empty[s]);
         }
       };
       // K and V of the same entries, entry by entry in the order the producer fills them
       auto skip_both = [&](int from, int to) {
-        for (int w = from; ok && w < to; ++w) {
-          skip_k(w, w + 1);
-          skip_v(w, w + 1);
+        for (int e = from; ok && e < to; ++e) {
+          skip_k(e, e + 1);
+          skip_v(e, e + 1);
         }
       };
-      // S(j) = Q K^T for the tile's j-th entry, into S buffer j & 1; the K stage goes back to the producer
-      // when these MMAs have read it
+      // the MMAs of S(j) = Q K^T for the tile's j-th entry, into S buffer (sbase + j) & 1 (issuing lane only)
+      auto qk_mmas = [&](int j, int s) {
+        const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
+        const uint32_t buf = (sbase + (uint32_t)j) & 1u;
+        const uint32_t s_tmem = tmem + col_s(x, buf);
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+          // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
+          const uint32_t half = kk >> 2, off = (kk & 3) * 32;
+          tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
+                    k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
+        }
+        tc_commit(&ctl->s_full[x][buf]);
+        tc_commit(&k_empty[s]);   // the K stage goes back to the producer when these MMAs have read it
+        if (PERSISTENT && j == seen.total - 1) tc_commit(&ctl->q_empty[x]);   // the super-tile's last read of this tile's Q
+      };
       auto issue_qk = [&](int j) {
-        const int u = seen.entry(j);
-        const int s = u & (kStages - 1);
-        wait(&ctl->k_full[s], (u / kStages) & 1, kWaitKFull);
+        const uint32_t g = ring + (uint32_t)seen.entry(j);
+        const int s = g & (kStages - 1);
+        wait(&ctl->k_full[s], (g / kStages) & 1, kWaitKFull);
         if (!ok) return;
         tc_fence_after();
-        if (elect_one()) {
-          const uint64_t k_desc = k_desc0 + (uint64_t)(s * (kKBytes >> 4));
-          const uint32_t s_tmem = tmem + col_s(x, j & 1);
-#pragma unroll
-          for (int kk = 0; kk < DH / 16; ++kk) {
-            // 16 dims per step: 32 B inside the swizzle row; dims 64-127 sit in the second half-tile
-            const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-            tc_mma_ss(s_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
-                      k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
-          }
-          tc_commit(&ctl->s_full[x][j & 1]);
-          tc_commit(&k_empty[s]);
-        }
+        if (elect_one()) qk_mmas(j, s);
         __syncwarp();
       };
 
       if (seen.total > 0) {
         skip_both(0, seen.entry(0));
-        if (ok) wait(&ctl->q_full, 0, kWaitQ);
+        if (ok) wait(&ctl->q_full, n & 1, kWaitQ);
         if (ok) issue_qk(0);
         if (ok && seen.total > 1) {
           skip_k(seen.entry(0) + 1, seen.entry(1));
           if (ok) issue_qk(1);
         }
       } else {
+        if (PERSISTENT) {
+          if (elect_one()) mbar_arrive(&ctl->q_empty[x]);   // this tile reads no Q in this super-tile
+          __syncwarp();
+        }
         skip_both(0, nkv);
       }
       // Per step: everything that can be checked before P arrives is (V of this step, K of the S two steps
@@ -534,18 +679,25 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (i > 0 && u != u_prev + 1) skip_v(u_prev + 1, u);
         if (ok && ahead && u2 != u1 + 1) skip_k(u1 + 1, u2);
         if (!ok) break;
-        const int sv = u & (kStages - 1), sk = u2 & (kStages - 1);
+        const uint32_t gv = ring + (uint32_t)u, gk = ring + (uint32_t)(ahead ? u2 : 0);
+        const int sv = gv & (kStages - 1), sk = gk & (kStages - 1);
+        const uint32_t gs = sbase + (uint32_t)i, buf = gs & 1u, ppar = (gs >> 1) & 1u;
+        // operands of this step's MMAs, ready before the polls: between "P has arrived" and the MMAs being
+        // queued nothing should be left to compute
+        const uint64_t v_desc = v_desc0 + (uint64_t)(sv * (kKBytes >> 4));
+        const uint32_t sp_tmem = tmem + col_s(x, buf);
+        const bool last_pv_but_one = i + 2 == seen.total;
         {
           // The TMA operands are normally there already, and so is P by the time the issuer comes back from
           // queueing the previous batch: one poll of each barrier, issued back to back, and one vote.
-          const bool v_there = mbar_try_wait(&ctl->v_full[sv], (u / kStages) & 1);
-          const bool k_there = !ahead || mbar_try_wait(&ctl->k_full[sk], (u2 / kStages) & 1);
-          const bool p_there = mbar_try_wait(&ctl->p_full[x][i & 1], (i >> 1) & 1);
+          const bool v_there = mbar_try_wait(&ctl->v_full[sv], (gv / kStages) & 1);
+          const bool k_there = !ahead || mbar_try_wait(&ctl->k_full[sk], (gk / kStages) & 1);
+          const bool p_there = mbar_try_wait(&ctl->p_full[x][buf], ppar);
           if (!__all_sync(0xffffffffu, v_there && k_there && p_there)) {
-            wait(&ctl->v_full[sv], (u / kStages) & 1, kWaitVFull);
-            if (ok && ahead) wait(&ctl->k_full[sk], (u2 / kStages) & 1, kWaitKFull);
-            // P(i) is in TMEM (first half of S buffer i & 1) and O has been rescaled if it had to be
-            if (ok) wait(&ctl->p_full[x][i & 1], (i >> 1) & 1, kWaitP);
+            wait(&ctl->v_full[sv], (gv / kStages) & 1, kWaitVFull);
+            if (ok && ahead) wait(&ctl->k_full[sk], (gk / kStages) & 1, kWaitKFull);
+            // P(i) is in TMEM (first half of its S buffer) and O has been rescaled if it had to be
+            if (ok) wait(&ctl->p_full[x][buf], ppar, kWaitP);
             if (!ok) break;
           }
         }
@@ -557,28 +709,16 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         tc_fence_after();
         if (elect_one()) {
-          const uint64_t v_desc = v_desc0 + (uint64_t)(sv * (kKBytes >> 4));
-          const uint32_t sp_tmem = tmem + col_s(x, i & 1);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
             // V is MN-major: 16 tokens = two 8-row groups (2048 B); dims 64-127 live kKBytes/2 further on
             tc_mma_ts(o_tmem, sp_tmem + kk * 8, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
           }
           // "O is quiet" is normally read off the next S (see the softmax side); the last step has no such S
-          if (i + 2 == seen.total) tc_commit(&ctl->pv_done[x]);
+          if (last_pv_but_one) tc_commit(&ctl->pv_done[x]);
           tc_commit(&v_empty[sv]);   // the V stage goes back to the producer when these MMAs have read it
-          if (ahead) {
-            // S(i+2) into the buffer P(i) is being read from: behind O += P(i) V(i) in this thread's order
-            const uint64_t k_desc = k_desc0 + (uint64_t)(sk * (kKBytes >> 4));
-#pragma unroll
-            for (int kk = 0; kk < DH / 16; ++kk) {
-              const uint32_t half = kk >> 2, off = (kk & 3) * 32;
-              tc_mma_ss(sp_tmem, q_desc + (uint64_t)((half * (kQBytes / 2) + off) >> 4),
-                        k_desc + (uint64_t)((half * (kKBytes / 2) + off) >> 4), idesc_qk, kk > 0);
-            }
-            tc_commit(&ctl->s_full[x][i & 1]);
-            tc_commit(&k_empty[sk]);
-          }
+          // S(i+2) into the buffer P(i) is being read from: behind O += P(i) V(i) in this thread's order
+          if (ahead) qk_mmas(i + 2, sk);
           pipe_release(ctl);
         }
         __syncwarp();
@@ -591,149 +731,182 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         __syncwarp();
         skip_both(seen.entry(seen.total - 1) + 1, nkv);
       }
+      ring += (uint32_t)nkv;
+      sbase += (uint32_t)seen.total;
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int x = warp >> 2;                              // which query tile this warpgroup owns
-    const int tq = t0 + x;
-    const TileSeen seen = tile_seen(x == 0 || active1, tq, tb, nb, local_b);
     const int row = tid & 127;                            // tile row == TMEM lane
-    const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
-    const int bi = (int)(i_tok >> 6);
-    const int lo_band = bi + 1 - local_b;                 // first band block this row sees
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-
-    float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
-    float l = 0.f;
+    uint32_t sbase = 0;    // S/P buffers this tile has used before this super-tile
+    uint32_t n_pv = 0;     // completed phases of pv_done[x]: super-tiles in which this tile had two or more entries
+    uint32_t n_o = 0;      // completed phases of o_full[x]: super-tiles in which this tile had any entry
     bool ok = true;
 
-    for (int i = 0; i < seen.total; ++i) {
-      const int jb = tb.block(seen.entry(i));
-      ok = mbar_wait(&ctl->s_full[x][i & 1], (i >> 1) & 1, ctl, p.status, kWaitS);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t sv[64];
-      {
-        uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
-        uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
-        tmem_ld32(lane_base + col_s(x, i & 1), lo32);
-        tmem_ld32(lane_base + col_s(x, i & 1) + 32, hi32);
-        tmem_wait_ld();
+    for (uint32_t n = 0; ok; ++n) {
+      int unit = (int)blockIdx.x;
+      if (PERSISTENT) {
+        const int slot = n & 1;
+        ok = mbar_wait(&ctl->tile_full[slot], (n >> 1) & 1, ctl, p.status, kWaitTile);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        unit = *(volatile int*)&ctl->tile_id[slot];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->tile_empty[slot]);
+        if (unit < 0) break;
+      } else if (n > 0) {
+        break;
       }
-      const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
-      if (edge) {
-        const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
-        const int64_t j0 = (int64_t)jb * kBN;
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const bool vis = row_sees && (j0 + c <= i_tok) && (j0 + c < p.N);
-          if (!vis) sv[c] = 0xff800000u;  // -inf
-        }
-      }
-      // row max of the raw scores, four independent chains of three-input max
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) mx[r] = fmax3(mx[r], __uint_as_float(sv[c + 2 * r]), __uint_as_float(sv[c + 2 * r + 1]));
-      }
-      // scale_log2 > 0, so the max commutes with the scaling
-      const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
-      // lazy rescale: move the reference max only when it grew by more than 2^8
-      float factor = 1.f;
-      if (mt > m_used + kLazyMaxSlack) {
-        factor = (m_used == -INFINITY) ? 1.f : exp2f(m_used - mt);
-        m_used = mt;
-      }
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      uint32_t pk[32];
-      // scaling, max subtraction and the row sum on packed pairs (one issue slot for two values)
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
-      float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, nm2);
-        const float2 p2 = make_float2(exp2f(x2.x), exp2f(x2.y));
-        ls2[(c >> 1) & 1] = __fadd2_rn(ls2[(c >> 1) & 1], p2);
-        // P has the tensors' dtype (the MMA wants A and B in one format): with bf16 its 8-bit mantissa is the
-        // largest rounding error of the bf16 path
-        pk[c >> 1] = Cvt<T>::pack(p2.x, p2.y);
-      }
-      l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
-      // P row -> TMEM, over the first half of the S buffer it came from (two values per column, even key in
-      // the low half).  The buffer's previous reader, P.V(i-2), finished before S(i) was written into it.
-      tmem_st32(lane_base + col_s(x, i & 1), pk);
-      if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-        // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished.  S(i+1)
-        // was issued right behind it by the same thread, so "S(i+1) complete" says so; the last step has no
-        // next S and gets a commit of its own.
-        ok = (i + 1 < seen.total)
-                 ? mbar_wait(&ctl->s_full[x][(i + 1) & 1], ((i + 1) >> 1) & 1, ctl, p.status, kWaitS)
-                 : mbar_wait(&ctl->pv_done[x], 0, ctl, p.status, kWaitPV);
+      const TileWork w = (n == 0) ? w_first : tile_work<true>(unit, p);
+      const int tq = w.t0 + x;
+      const TileSeen seen = tile_seen(x == 0 || w.active1, tq, w.tb, w.nb, w.local_b);
+      const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
+      const int bi = (int)(i_tok >> 6);
+      const int lo_band = bi + 1 - w.local_b;               // first band block this row sees
+      const int sink_b = w.sink_b, local_b = w.local_b;
+
+      float m_used = -INFINITY;  // max the exponentials are taken against (log2 units)
+      float l = 0.f;
+
+      for (int i = 0; i < seen.total; ++i) {
+        const int jb = w.tb.block(seen.entry(i));
+        const uint32_t gs = sbase + (uint32_t)i, buf = gs & 1u;
+        ok = mbar_wait(&ctl->s_full[x][buf], (gs >> 1) & 1u, ctl, p.status, kWaitS);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        uint32_t sv[64];
+        {
+          uint32_t (&lo32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+          uint32_t (&hi32)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+          tmem_ld32(lane_base + col_s(x, buf), lo32);
+          tmem_ld32(lane_base + col_s(x, buf) + 32, hi32);
+          tmem_wait_ld();
+        }
+        const bool edge = (jb >= 2 * tq) || (jb >= sink_b && jb == 2 * tq + 1 - local_b);
+        if (edge) {
+          // key c of the block is visible iff the row sees the block at all, c <= query - j0 (causal) and
+          // c < N - j0 (inside the sequence): one 32-bit limit per row, one compare and select per key
+          const bool row_sees = (jb <= bi) && (jb < sink_b || jb >= lo_band);
+          const int64_t j0 = (int64_t)jb * kBN;
+          const int64_t lim64 = min(i_tok - j0, p.N - 1 - j0);
+          const int limit = row_sees ? (int)max((int64_t)-1, min(lim64, (int64_t)63)) : -1;
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            if (c > limit) sv[c] = 0xff800000u;  // -inf
+          }
+        }
+        // row max of the raw scores, four independent chains of three-input max
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) mx[r] = fmax3(mx[r], __uint_as_float(sv[c + 2 * r]), __uint_as_float(sv[c + 2 * r + 1]));
+        }
+        // scale_log2 > 0, so the max commutes with the scaling
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        // lazy rescale: move the reference max only when it grew by more than 2^8
+        float factor = 1.f;
+        if (mt > m_used + kLazyMaxSlack) {
+          factor = (m_used == -INFINITY) ? 1.f : exp2f(m_used - mt);
+          m_used = mt;
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        uint32_t pk[32];
+        // scaling, max subtraction and the row sum on packed pairs (one issue slot for two values)
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), sc2, nm2);
+          const float2 p2 = make_float2(exp2f(x2.x), exp2f(x2.y));
+          ls2[(c >> 1) & 1] = __fadd2_rn(ls2[(c >> 1) & 1], p2);
+          // P has the tensors' dtype (the MMA wants A and B in one format): with bf16 its 8-bit mantissa is the
+          // largest rounding error of the bf16 path
+          pk[c >> 1] = Cvt<T>::pack(p2.x, p2.y);
+        }
+        l = fmaf(l, factor, (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y));
+        // P row -> TMEM, over the first half of the S buffer it came from (two values per column, even key in
+        // the low half).  The buffer's previous reader, P.V(i-2), finished before S(i) was written into it.
+        tmem_st32(lane_base + col_s(x, buf), pk);
+        if (i > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+          // O may only be touched when P.V(i-1), the last MMA that accumulates into it, has finished.  S(i+1)
+          // was issued right behind it by the same thread, so "S(i+1) complete" says so; the last step has no
+          // next S and gets a commit of its own.
+          ok = (i + 1 < seen.total)
+                   ? mbar_wait(&ctl->s_full[x][(gs + 1) & 1u], ((gs + 1) >> 1) & 1u, ctl, p.status, kWaitS)
+                   : mbar_wait(&ctl->pv_done[x], n_pv & 1u, ctl, p.status, kWaitPV);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < DH; c0 += 32) {
+            uint32_t ov[32];
+            tmem_ld32(lane_base + col_o(x) + c0, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
+            tmem_st32(lane_base + col_o(x) + c0, ov);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&ctl->p_full[x][buf]);
+      }
+      if (!ok) break;
+
+      if (seen.total == 0 && (x == 0 || w.active1) && i_tok < p.N) {
+        // a tile that sees no key at all (no sink block and no window block): its rows are zero, like the rows
+        // of a visible tile whose own mask is empty
+        uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+                        ((int64_t)w.b * p.o_sb + i_tok * p.o_sn + (int64_t)w.h * p.o_sh) * (OUT_F32 ? 4 : 2);
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+        for (int c = 0; c < DH * (OUT_F32 ? 4 : 2); c += 16) *reinterpret_cast<uint4*>(orow + c) = z;
+      }
+      if (seen.total > 0) {
+        ok = mbar_wait(&ctl->o_full[x], n_o & 1u, ctl, p.status, kWaitO);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        const bool store = i_tok < p.N;
+        uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+                        ((int64_t)w.b * p.o_sb + i_tok * p.o_sn + (int64_t)w.h * p.o_sh) * (OUT_F32 ? 4 : 2);
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 32) {
           uint32_t ov[32];
           tmem_ld32(lane_base + col_o(x) + c0, ov);
           tmem_wait_ld();
+          if (store) {
+            if (OUT_F32) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * factor);
-          tmem_st32(lane_base + col_o(x) + c0, ov);
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&ctl->p_full[x][i & 1]);
-    }
-
-    if (seen.total == 0 && (x == 0 || active1) && i_tok < p.N) {
-      // a tile that sees no key at all (no sink block and no window block): its rows are zero, like the rows
-      // of a visible tile whose own mask is empty
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      ((int64_t)b * p.o_sb + i_tok * p.o_sn + (int64_t)h * p.o_sh) * (OUT_F32 ? 4 : 2);
-      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 1
-      for (int c = 0; c < DH * (OUT_F32 ? 4 : 2); c += 16) *reinterpret_cast<uint4*>(orow + c) = z;
-    }
-    if (ok && seen.total > 0) {
-      ok = mbar_wait(&ctl->o_full[x], 0, ctl, p.status, kWaitO);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok && seen.total > 0) {
-      tc_fence_after();
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      const bool store = i_tok < p.N;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      ((int64_t)b * p.o_sb + i_tok * p.o_sn + (int64_t)h * p.o_sh) * (OUT_F32 ? 4 : 2);
-#pragma unroll 1
-      for (int c0 = 0; c0 < DH; c0 += 32) {
-        uint32_t ov[32];
-        tmem_ld32(lane_base + col_o(x) + c0, ov);
-        tmem_wait_ld();
-        if (store) {
-          if (OUT_F32) {
+              for (int c = 0; c < 32; c += 4) {
+                float4 f = make_float4(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l,
+                                       __uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
+                *reinterpret_cast<float4*>(orow + (c0 + c) * 4) = f;
+              }
+            } else {
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-              float4 f = make_float4(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l,
-                                     __uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
-              *reinterpret_cast<float4*>(orow + (c0 + c) * 4) = f;
-            }
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 uo;
-              uo.x = Cvt<T>::pack(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l);
-              uo.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
-              uo.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
-              uo.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = uo;
+              for (int c = 0; c < 32; c += 8) {
+                uint4 uo;
+                uo.x = Cvt<T>::pack(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l);
+                uo.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
+                uo.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
+                uo.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = uo;
+              }
             }
           }
         }
+        // the next super-tile's first O += P V overwrites O; it is issued only after every thread of this
+        // tile has arrived with its first P, i.e. after these loads
+        tc_fence_before();
       }
+      sbase += (uint32_t)seen.total;
+      n_pv += seen.total >= 2 ? 1u : 0u;
+      n_o += seen.total > 0 ? 1u : 0u;
     }
   }
 
@@ -800,10 +973,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int64_
   return MOA_OK;
 }
 
-template <typename T, bool F32, int DH>
+template <typename T, bool F32, int DH, bool PERSISTENT>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
                    dim3 grid, cudaStream_t stream) {
-  auto kern = moa_prefill_kernel<T, F32, DH>;
+  auto kern = moa_prefill_kernel<T, F32, DH, PERSISTENT>;
   // The shared-memory opt-in is a per-device attribute of the function: keep the "done" flag per device
   // ordinal (one process may drive several GPUs) and per instantiation.
   constexpr int kMaxDevices = 64;
@@ -829,8 +1002,7 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
                                int dtype, int out_f32, int32_t* status, moa_stream_t stream) {
   using namespace moa;
   MOA_REQUIRE(q && k && v && out && sink_blocks && local_blocks && status, "prefill: null pointer");
-  MOA_REQUIRE(B > 0 && H > 0 && N > 0 && B <= 65535, "prefill: bad shape");
-  MOA_REQUIRE((N + 255) / 256 < 148 || H <= 65535, "prefill: too many heads for one launch");
+  MOA_REQUIRE(B > 0 && H > 0 && N > 0, "prefill: bad shape");
   MOA_REQUIRE(N < (1LL << 31) - 512, "prefill: sequence too long");
   MOA_REQUIRE(sm_scale > 0.f, "prefill: sm_scale must be positive");
   if (D != 64 && D != 128) {
@@ -856,24 +1028,66 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   p.out = out; p.o_sb = o_sb; p.o_sn = o_sn; p.o_sh = o_sh;
   p.sink_blocks = sink_blocks; p.local_blocks = local_blocks;
   p.B = B; p.H = H; p.N = N; p.scale_log2 = sm_scale * 1.4426950408889634f; p.status = status;
-  const int nsuper = (int)((N + 2 * kBM - 1) / (2 * kBM));
-  // fewer super-tiles per head than SMs, and K and V together not much larger than L2 (126 MB): interleave the
-  // heads.  Measured with 32 heads: +12 % at 8192 tokens (134 MB of K/V), -4 % at 16384 (268 MB).
+  const int64_t nsuper = (N + 2 * kBM - 1) / (2 * kBM);
+  MOA_REQUIRE(nsuper * H * B < (1LL << 30), "prefill: too many query tiles for one launch");
+  p.nsuper = (int)nsuper;
+  p.num_tiles = (int)(nsuper * H * B);
+  // Units are handed out in chunks of consecutive super-tiles per head (tile_coord).  Small chunks end the launch
+  // on cheap tiles; large ones keep the blocks that run at the same time on few heads, whose K/V bands then stay
+  // in L2 (126 MB).  Measured with 32 heads against one head after the other: 8192 tokens (134 MB of K and V)
+  // chunk 2 +16 %, 16384 tokens (268 MB) chunk 4 +3 % and chunk 2 -1 %, 32768 tokens (537 MB) chunk 16 -2 %,
+  // 65536 tokens chunk 16 -2 % and chunk 2 -11 %.
   const int64_t kv_bytes = (int64_t)B * H * N * D * 2 * 2;
-  p.heads_fastest = (nsuper < 148 && H <= 65535 && kv_bytes <= (160ll << 20)) ? 1 : 0;
-  dim3 grid = p.heads_fastest ? dim3((unsigned)H, (unsigned)nsuper, (unsigned)B)
-                              : dim3((unsigned)nsuper, (unsigned)H, (unsigned)B);
+#ifdef MOA_PREFILL_CHUNK
+  p.chunk = (int)(MOA_PREFILL_CHUNK < 1 ? 1 : (MOA_PREFILL_CHUNK > nsuper ? nsuper : MOA_PREFILL_CHUNK));
+#else
+  p.chunk = kv_bytes <= (96ll << 20) ? 1 : kv_bytes <= (192ll << 20) ? 2 : kv_bytes <= (384ll << 20) ? 4 : (int)nsuper;
+  if (p.chunk > nsuper) p.chunk = (int)nsuper;
+#endif
+  // one block per SM (shared memory and TMEM allow no more), fewer when there are fewer super-tiles
+  int sms = 0;
+  {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices];
+    int dev = -1;
+    MOA_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) {
+      sms = cached[dev];
+    } else {
+      MOA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      if (dev >= 0 && dev < kMaxDevices) cached[dev] = sms;
+    }
+  }
+  MOA_REQUIRE(sms > 0, "prefill: no multiprocessors reported");
+  // Which form: up to 16384 tokens of 32 heads (K and V up to 384 MB) the persistent one wins (4096: +8 %,
+  // 16384: +5 % against one block per unit); beyond that one block per unit does (65536: +1 %), and so it does
+  // when there are not even two units per SM (2048 tokens of 32 heads: +4 %; the launch then ends when the
+  // heaviest unit does, whoever runs the rest).
+#ifdef MOA_PREFILL_PERSISTENT
+  const bool persistent = MOA_PREFILL_PERSISTENT != 0;
+#else
+  const bool persistent = kv_bytes <= (384ll << 20) && p.num_tiles > 2 * sms;
+#endif
+  dim3 grid((unsigned)(persistent && sms < p.num_tiles ? sms : p.num_tiles));
   cudaStream_t st = (cudaStream_t)stream;
-  const int variant = (dtype == MOA_BF16 ? 4 : 0) + (out_f32 ? 2 : 0) + (D == 64 ? 1 : 0);
+  const int variant = (persistent ? 8 : 0) + (dtype == MOA_BF16 ? 4 : 0) + (out_f32 ? 2 : 0) + (D == 64 ? 1 : 0);
   switch (variant) {
-    case 0: return launch_prefill<__half, false, 128>(mq, mk, mv, p, grid, st);
-    case 1: return launch_prefill<__half, false, 64>(mq, mk, mv, p, grid, st);
-    case 2: return launch_prefill<__half, true, 128>(mq, mk, mv, p, grid, st);
-    case 3: return launch_prefill<__half, true, 64>(mq, mk, mv, p, grid, st);
-    case 4: return launch_prefill<__nv_bfloat16, false, 128>(mq, mk, mv, p, grid, st);
-    case 5: return launch_prefill<__nv_bfloat16, false, 64>(mq, mk, mv, p, grid, st);
-    case 6: return launch_prefill<__nv_bfloat16, true, 128>(mq, mk, mv, p, grid, st);
-    default: return launch_prefill<__nv_bfloat16, true, 64>(mq, mk, mv, p, grid, st);
+    case 0: return launch_prefill<__half, false, 128, false>(mq, mk, mv, p, grid, st);
+    case 1: return launch_prefill<__half, false, 64, false>(mq, mk, mv, p, grid, st);
+    case 2: return launch_prefill<__half, true, 128, false>(mq, mk, mv, p, grid, st);
+    case 3: return launch_prefill<__half, true, 64, false>(mq, mk, mv, p, grid, st);
+    case 4: return launch_prefill<__nv_bfloat16, false, 128, false>(mq, mk, mv, p, grid, st);
+    case 5: return launch_prefill<__nv_bfloat16, false, 64, false>(mq, mk, mv, p, grid, st);
+    case 6: return launch_prefill<__nv_bfloat16, true, 128, false>(mq, mk, mv, p, grid, st);
+    case 7: return launch_prefill<__nv_bfloat16, true, 64, false>(mq, mk, mv, p, grid, st);
+    case 8: return launch_prefill<__half, false, 128, true>(mq, mk, mv, p, grid, st);
+    case 9: return launch_prefill<__half, false, 64, true>(mq, mk, mv, p, grid, st);
+    case 10: return launch_prefill<__half, true, 128, true>(mq, mk, mv, p, grid, st);
+    case 11: return launch_prefill<__half, true, 64, true>(mq, mk, mv, p, grid, st);
+    case 12: return launch_prefill<__nv_bfloat16, false, 128, true>(mq, mk, mv, p, grid, st);
+    case 13: return launch_prefill<__nv_bfloat16, false, 64, true>(mq, mk, mv, p, grid, st);
+    case 14: return launch_prefill<__nv_bfloat16, true, 128, true>(mq, mk, mv, p, grid, st);
+    default: return launch_prefill<__nv_bfloat16, true, 64, true>(mq, mk, mv, p, grid, st);
   }
 }
 

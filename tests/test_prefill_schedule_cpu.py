@@ -303,3 +303,274 @@ def test_the_model_catches_a_single_p_barrier():
         except AssertionError as exc:
             caught += "p_full" in str(exc)
     assert caught > 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# The persistent form: one block works through a sequence of super-tiles.  Every role keeps running counts
+# (ring entries, S/P buffers, phases of the per-super-tile barriers), the producer publishes the next
+# super-tile through a two-entry ring and runs ahead.  Same model as above, over a whole sequence, with the
+# barriers that only exist across super-tiles (tile_full / tile_empty, q_full / q_empty, pv_done, o_full).
+# ---------------------------------------------------------------------------------------------------
+class CountBarrier(Barrier):
+    def __init__(self, name, count):
+        super().__init__(name)
+        self.count, self.pending = count, 0
+
+    def arrive(self):
+        self.pending += 1
+        if self.pending == self.count:
+            self.pending, self.done = 0, self.done + 1
+
+
+def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
+    """units: [(n, sink_b, local_b, st), ...] in the order one block receives them."""
+
+    def hand_back(bar):
+        if isinstance(bar, CountBarrier):
+            bar.arrive()
+        else:
+            bar.done += 1
+
+    work = [lists(n, s, l, st) for n, s, l, st in units]
+    kfull = [Barrier(f"k_full[{s}]") for s in range(STAGES)]
+    vfull = [Barrier(f"v_full[{s}]") for s in range(STAGES)]
+    kempty = [[Barrier(f"k_empty[{x}][{s}]") for s in range(STAGES)] for x in range(2)]
+    vempty = [[Barrier(f"v_empty[{x}][{s}]") for s in range(STAGES)] for x in range(2)]
+    sfull = [[Barrier(f"s_full[{x}][{b}]") for b in range(2)] for x in range(2)]
+    pfull = [[Barrier(f"p_full[{x}][{b}]") for b in range(2)] for x in range(2)]
+    pvdone = [Barrier(f"pv_done[{x}]") for x in range(2)]
+    ofull = [Barrier(f"o_full[{x}]") for x in range(2)]
+    qfull = Barrier("q_full")
+    qempty = [Barrier(f"q_empty[{x}]") for x in range(2)] if q_empty_per_issuer else [CountBarrier("q_empty", 2)] * 2
+    tfull = [Barrier(f"tile_full[{s}]") for s in range(2)]
+    tempty = [CountBarrier(f"tile_empty[{s}]", 4) for s in range(2)]     # 2 issuers + 2 softmax groups
+    slot_value = [None, None]
+    finished = {"o_read": [0, 0], "o_written_first": [0, 0]}
+
+    def wait(bar, need):
+        while not bar.look(need):
+            yield
+
+    def producer():
+        ring = 0
+        for n in range(len(units) + 1):
+            unit = n if n < len(units) else -1
+            slot = n & 1
+            if n > 0 and q_wait_first:                           # both issuers are done with the previous Q
+                while not (qempty[0].look(n) and qempty[1].look(n)):
+                    yield
+            yield from wait(tempty[slot], n >> 1)                # phase (n >> 1) of the slot's "empty" complete
+            slot_value[slot] = unit
+            tfull[slot].done += 1
+            if unit < 0:
+                return
+            nkv = work[unit][2]
+            if n > 0 and not q_wait_first:
+                while not (qempty[0].look(n) and qempty[1].look(n)):
+                    yield
+            qfull.done += 1
+            for u in range(nkv + 1):
+                if u < nkv:
+                    g = ring + u
+                    while not (kempty[0][g % STAGES].look(g // STAGES) and kempty[1][g % STAGES].look(g // STAGES)):
+                        yield
+                    kfull[g % STAGES].done += 1
+                if u >= 1:
+                    g = ring + u - 1
+                    while not (vempty[0][g % STAGES].look(g // STAGES) and vempty[1][g % STAGES].look(g // STAGES)):
+                        yield
+                    vfull[g % STAGES].done += 1
+            ring += nkv
+
+    def take_unit(n):
+        slot = n & 1
+        yield from wait(tfull[slot], (n >> 1) + 1)
+        unit = slot_value[slot]
+        tempty[slot].arrive()
+        return unit
+
+    def issuer(x):
+        ring = sbase = 0
+        n = 0
+        while True:
+            unit = yield from take_unit(n)
+            if unit < 0:
+                return
+            tb, seen, nkv = work[unit]
+            sn, total = seen[x], len(seen[x])
+
+            def skip(kind, a, b):
+                for e in range(a, b):
+                    g = ring + e
+                    full, empty = (kfull, kempty) if kind == "k" else (vfull, vempty)
+                    yield from wait(full[g % STAGES], g // STAGES + 1)
+                    empty[x][g % STAGES].done += 1
+
+            def skip_both(a, b):
+                for e in range(a, b):
+                    yield from skip("k", e, e + 1)
+                    yield from skip("v", e, e + 1)
+
+            def qk_mmas(j, g):
+                gs = sbase + j
+                sfull[x][gs & 1].done += 1
+                kempty[x][g % STAGES].done += 1
+                if j == total - 1:
+                    hand_back(qempty[x])
+
+            def issue_qk(j):
+                g = ring + sn[j]
+                yield from wait(kfull[g % STAGES], g // STAGES + 1)
+                qk_mmas(j, g)
+
+            if total > 0:
+                yield from skip_both(0, sn[0])
+                yield from wait(qfull, n + 1)
+                yield from issue_qk(0)
+                if total > 1:
+                    yield from skip("k", sn[0] + 1, sn[1])
+                    yield from issue_qk(1)
+            else:
+                hand_back(qempty[x])
+                yield from skip_both(0, nkv)
+            u_prev, u, u1 = -1, (sn[0] if total > 0 else -1), (sn[1] if total > 1 else -1)
+            for i in range(total):
+                ahead = i + 2 < total
+                u2 = sn[i + 2] if ahead else -1
+                if i > 0 and u != u_prev + 1:
+                    yield from skip("v", u_prev + 1, u)
+                if ahead and u2 != u1 + 1:
+                    yield from skip("k", u1 + 1, u2)
+                gv = ring + u
+                yield from wait(vfull[gv % STAGES], gv // STAGES + 1)
+                if ahead:
+                    gk = ring + u2
+                    yield from wait(kfull[gk % STAGES], gk // STAGES + 1)
+                gs = sbase + i
+                yield from wait(pfull[x][gs & 1], (gs >> 1) + 1)
+                if i == 0:
+                    # the first O += P V of a super-tile overwrites O: the previous epilogue must have read it
+                    assert finished["o_read"][x] == finished["o_written_first"][x], "O overwritten before it was read"
+                    finished["o_written_first"][x] += 1
+                if i + 2 == total:
+                    pvdone[x].done += 1
+                vempty[x][gv % STAGES].done += 1
+                if ahead:
+                    qk_mmas(i + 2, ring + u2)
+                u_prev, u, u1 = u, u1, u2
+            if total > 0:
+                ofull[x].done += 1
+                yield from skip_both(sn[-1] + 1, nkv)
+            ring += nkv
+            sbase += total
+            n += 1
+
+    def softmax(x):
+        sbase = n_pv = n_o = 0
+        n = 0
+        while True:
+            unit = yield from take_unit(n)
+            if unit < 0:
+                return
+            total = len(work[unit][1][x])
+            for i in range(total):
+                gs = sbase + i
+                yield from wait(sfull[x][gs & 1], (gs >> 1) + 1)
+                if i > 0 and rng.randint(3) == 0:
+                    if i + 1 < total:
+                        yield from wait(sfull[x][(gs + 1) & 1], ((gs + 1) >> 1) + 1)
+                    else:
+                        yield from wait(pvdone[x], n_pv + 1)
+                pfull[x][gs & 1].done += 1
+            if total > 0:
+                yield from wait(ofull[x], n_o + 1)
+                finished["o_read"][x] += 1
+            sbase += total
+            n_pv += 1 if total >= 2 else 0
+            n_o += 1 if total > 0 else 0
+            n += 1
+
+    agents = [producer(), issuer(0), issuer(1), softmax(0), softmax(1)]
+    alive = list(range(len(agents)))
+    everything = (kfull, vfull, kempty, vempty, sfull, pfull, [pvdone], [ofull], [[qfull] + qempty], [tfull], [tempty])
+    idle_rounds = 0
+    while alive:
+        k = alive[rng.randint(len(alive))]
+        before = _snapshot(*everything)
+        try:
+            next(agents[k])
+        except StopIteration:
+            alive.remove(k)
+        idle_rounds = idle_rounds + 1 if _snapshot(*everything) == before else 0
+        assert idle_rounds < 6000, "nobody makes progress"
+    assert finished["o_read"] == finished["o_written_first"]
+
+
+def test_persistent_sequence_of_super_tiles_keeps_every_barrier_unambiguous():
+    """Random sequences of super-tiles of different heads and lengths through one block, under random schedules:
+    no wait may ever be ambiguous (a barrier two phases ahead of its waiter), nobody may stall, and O is never
+    overwritten before the previous epilogue has read it.  Includes super-tiles in which one tile or both see
+    nothing, single-entry tiles, and ragged last super-tiles."""
+    shapes = [(4096, 1, 100), (4096, 1, 7), (2048, 2, 3), (1000, 0, 2), (5000, 3, 16), (200, 1, 1), (64, 0, 0),
+              (700, 0, 0), (300, 1, 0), (129, 1, 1), (256, 1, 40)]
+    for seed in range(12):
+        rng = np.random.RandomState(100 + seed)
+        units = []
+        for _ in range(int(rng.randint(2, 9))):
+            n, s, l = shapes[rng.randint(len(shapes))]
+            units.append((n, s, l, int(rng.randint(-(-n // 256)))))
+        simulate_persistent(units, rng)
+
+
+def test_the_persistent_model_catches_a_shared_q_hand_back_barrier():
+    """With one "Q is free" barrier of count 2 shared by the two issuers, an issuer that has nothing to do in the
+    next super-tile arrives twice in a row and completes the phase on its own; the producer then overwrites Q
+    (and completes a second phase of q_full) while the other issuer still waits for the first (when, in addition,
+    the next super-tile is published before the hand-back has been seen).  The model must notice."""
+    units = [(700, 0, 0, 1), (64, 0, 0, 0), (2048, 2, 3, 4), (2048, 2, 3, 1)]
+    caught = 0
+    for seed in range(40):
+        try:
+            simulate_persistent(units, np.random.RandomState(seed), q_empty_per_issuer=False, q_wait_first=False)
+        except AssertionError as exc:
+            caught += "q_full" in str(exc)
+    assert caught > 0
+
+
+def test_the_persistent_model_catches_publishing_before_q_is_handed_back():
+    """If the producer published the next super-tile before it has seen "Q is free" for the previous one, an
+    issuer with nothing to do in the next one would hand Q back a second time first, and the producer's wait
+    would see a barrier two phases on.  The model must notice — this fixes the order in the kernel."""
+    units = [(4096, 1, 7, 9), (64, 0, 0, 0), (300, 1, 0, 0), (5000, 3, 16, 16)]
+    caught = 0
+    for seed in range(40):
+        try:
+            simulate_persistent(units, np.random.RandomState(seed), q_wait_first=False)
+        except AssertionError as exc:
+            caught += "q_empty" in str(exc)
+    assert caught > 0
+
+
+def tile_coord(unit, B, H, nsuper, chunk):
+    """The kernel's unit -> (batch, head, super-tile) map (``tile_coord`` in moa_b200/csrc/prefill.cu)."""
+    heads = B * H
+    per_chunk, full = heads * chunk, nsuper // chunk
+    k, width, r = unit // per_chunk, chunk, unit % per_chunk
+    if k >= full:
+        k, width, r = full, nsuper - full * chunk, unit - full * per_chunk
+    bh, j = r // width, r % width
+    return bh // H, bh % H, nsuper - 1 - k * chunk - j
+
+
+@pytest.mark.parametrize("B,H,nsuper,chunk", [(1, 32, 8, 1), (2, 3, 7, 3), (1, 32, 64, 4), (1, 5, 10, 10), (3, 2, 9, 4),
+                                              (1, 1, 1, 1), (1, 4, 5, 5), (2, 2, 6, 2), (1, 3, 11, 16 // 2)])
+def test_unit_order_covers_every_super_tile_once_heaviest_chunk_first(B, H, nsuper, chunk):
+    units = [tile_coord(u, B, H, nsuper, chunk) for u in range(B * H * nsuper)]
+    assert sorted(units) == sorted((b, h, st) for b in range(B) for h in range(H) for st in range(nsuper))
+    # chunks are handed out from the end of the sequence backwards: the chunk index never decreases ...
+    chunk_of = [(nsuper - 1 - st) // chunk for _, _, st in units]
+    assert chunk_of == sorted(chunk_of)
+    # ... and inside a chunk a head's super-tiles are consecutive and descending
+    for i in range(1, len(units)):
+        if units[i][:2] == units[i - 1][:2] and chunk_of[i] == chunk_of[i - 1]:
+            assert units[i][2] == units[i - 1][2] - 1
