@@ -669,13 +669,26 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     for i in range(warmup):
         step(i)
     ms, _ = time_blocks(step, steps, device, dist, min_blocks=3, min_region_s=0.2)
-    per_step_nccl = per_step = statistics.median(ms) / steps
+    per_step_eager = per_step_nccl = statistics.median(ms) / steps
+    pg = None
     if world > 1:        # the same steps with the gather done by the decode kernel (peer stores + barrier kernel)
         pg = model.model.enable_peer_gather(batch)
         for i in range(warmup):
             step(i)
         ms, _ = time_blocks(step, steps, device, dist, min_blocks=3, min_region_s=0.2)
-        per_step = statistics.median(ms) / steps
+        per_step_eager = statistics.median(ms) / steps
+    # the whole step captured once in a CUDA graph and replayed
+    graph = moa_b200.DecodeGraph(model, cache)
+
+    def step_graph(i):
+        graph.step(ids)
+
+    for i in range(warmup):
+        step_graph(i)
+    ms, _ = time_blocks(step_graph, steps, device, dist, min_blocks=3, min_region_s=0.2)
+    per_step = statistics.median(ms) / steps
+    del graph
+    if pg is not None:
         pg.check()
         pg.close()
     weights = sum(prm.numel() for name, prm in model.named_parameters()
@@ -683,7 +696,10 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
                         f"{layers} layers, heads sharded over {world} GPU(s)",
             "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
-            "ms_per_step_nccl_allgather": per_step_nccl,
+            "how": "one CUDA graph per decode step (all layers), gather by the decode kernel's peer stores" if world > 1
+                   else "one CUDA graph per decode step (all layers)",
+            "ms_per_step_eager_launches": per_step_eager,
+            "ms_per_step_eager_nccl_allgather": per_step_nccl if world > 1 else None,
             "kv_bytes_per_step_per_gpu": kv_bytes, "weight_bytes_per_step_per_gpu": weights,
             "hbm_gbs_per_gpu": (kv_bytes + weights) / (per_step * 1e-3) / 1e9}
 

@@ -246,7 +246,9 @@ int moa_rope_qk(void* q, void* k, int64_t sb, int64_t sh, int64_t sn, const void
  *   flag array and (2) waits until all `world` words of this rank's own array have reached `epoch`.
  *   flags: host array of `world` device pointers, flags[g] = rank g's array of `world` uint32 words (zero at
  *   the start; flags[rank] is this rank's own).  Every rank calls it with the same epoch, which must grow by
- *   one from call to call.  Work enqueued before the barrier on this stream (stores into the peers' buffers)
+ *   one from call to call; with epoch_counter given (a device uint32 of this rank, zero at the start) the
+ *   kernel counts the calls itself — it uses ++*epoch_counter and ignores `epoch` — so that the launch can be
+ *   captured in a CUDA graph and replayed.  Work enqueued before the barrier on this stream (stores into the peers' buffers)
  *   is visible to what the other ranks enqueue after theirs.  The wait gives up after limit_cycles SM cycles
  *   (at most 2e10): status (device int32[4], zero on entry) then holds {21, the rank waited for, epoch, rank}
  *   and the kernel returns normally.
@@ -257,8 +259,8 @@ int moa_peer_free(void* ptr);
 int moa_peer_export(void* ptr, void* handle);
 int moa_peer_open(const void* handle, void** ptr);
 int moa_peer_close(void* ptr);
-int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, int64_t limit_cycles, int32_t* status,
-                     moa_stream_t stream);
+int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, uint32_t* epoch_counter,
+                     int64_t limit_cycles, int32_t* status, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * moa_selftest_bounded_wait: failure-detection self-test (no counterpart in the reference, which has

@@ -11,7 +11,7 @@ from ._lib import LIB_PATH, MoaError  # noqa: F401  (loads the library, fails lo
 from .attention import check_device_status, mixture_of_sparse_attention, sparse_decode, sparse_prefill  # noqa: F401
 from .cache import StaticCircularCache  # noqa: F401
 from .dist import HeadSharding, PeerGather  # noqa: F401
-from .module import MoAAttention, MoALlamaForCausalLM, MoALlamaModel, update_model_function  # noqa: F401
+from .module import DecodeGraph, MoAAttention, MoALlamaForCausalLM, MoALlamaModel, update_model_function  # noqa: F401
 from .plan import (  # noqa: F401
     decode_bytes,
     load_plan,
@@ -29,5 +29,5 @@ __all__ = [
     "StaticCircularCache", "moa_config_to_cache_config", "moa_config_to_permutation",
     "permute_attention_projection", "permute_output_projection", "load_plan",
     "prefill_block_visits", "prefill_flops", "decode_bytes", "shard_heads", "MoaError", "LIB_PATH",
-    "MoAAttention", "MoALlamaModel", "MoALlamaForCausalLM", "update_model_function", "HeadSharding", "PeerGather",
+    "MoAAttention", "MoALlamaModel", "MoALlamaForCausalLM", "update_model_function", "HeadSharding", "PeerGather", "DecodeGraph",
 ]

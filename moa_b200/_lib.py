@@ -63,7 +63,7 @@ def _load() -> ctypes.CDLL:
     lib.moa_peer_export.argtypes = [P, P]
     lib.moa_peer_open.argtypes = [P, ctypes.POINTER(c_void_p)]
     lib.moa_peer_close.argtypes = [P]
-    lib.moa_peer_barrier.argtypes = [P, I, I, ctypes.c_uint32, I64, P, P]
+    lib.moa_peer_barrier.argtypes = [P, I, I, ctypes.c_uint32, P, I64, P, P]
     lib.moa_cache_append.argtypes = [P, P, P, P, I64, I64, P, P, P, P, P, I64, I, I, I, I64, I, P]
     lib.moa_cache_scan_mask.argtypes = [P, I64, P, P, I, I64, P]
     lib.moa_cache_fill.argtypes = [P, P, I64, I64, I64, P, P, P, P, P, P, P, P, P, I64, I, I, I64, I, I64, I64, I, P]

@@ -21,6 +21,7 @@ struct BarrierParams {
   uint32_t* flags[kMaxPeers];   // flags[g]: rank g's flag words (one per rank), mapped into this process
   int rank, world;
   uint32_t epoch;
+  uint32_t* epoch_counter;      // this rank's call counter in device memory, or nullptr: `epoch` is used
   long long limit_cycles;
   int32_t* status;              // int32[4]: [0] = 21 when the wait ran out, [1] = the rank waited for, [2] = epoch
 };
@@ -38,18 +39,30 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // Everything this rank's stream did before the barrier (the decode kernel's stores into the peers' buffers)
 // is ordered before the release; everything after the barrier on this stream follows the acquires.
 __global__ void peer_barrier_kernel(const BarrierParams p) {
+  __shared__ uint32_t epoch_shared;
   const int g = threadIdx.x;
+  if (g == 0) {
+    // The call's number: given by the host, or counted on the device (the form a CUDA graph can replay).
+    uint32_t e = p.epoch;
+    if (p.epoch_counter != nullptr) {
+      e = *p.epoch_counter + 1u;
+      *p.epoch_counter = e;
+    }
+    epoch_shared = e;
+  }
+  __syncthreads();
   if (g >= p.world) return;
+  const uint32_t epoch = epoch_shared;
   __threadfence_system();
-  st_release_sys(p.flags[g] + p.rank, p.epoch);
+  st_release_sys(p.flags[g] + p.rank, epoch);
   const uint32_t* mine = p.flags[p.rank] + g;
   const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
-    if ((int32_t)(ld_acquire_sys(mine) - p.epoch) >= 0) break;
+    if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) break;
     if ((spin & 63u) == 0 && clock64() - t0 > p.limit_cycles) {
       if (atomicCAS(&p.status[0], 0, 21) == 0) {
         p.status[1] = g;
-        p.status[2] = (int32_t)p.epoch;
+        p.status[2] = (int32_t)epoch;
         p.status[3] = p.rank;
       }
       break;
@@ -97,8 +110,8 @@ int moa_peer_close(void* ptr) {
   return MOA_OK;
 }
 
-int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, int64_t limit_cycles, int32_t* status,
-                     moa_stream_t stream) {
+int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, uint32_t* epoch_counter,
+                     int64_t limit_cycles, int32_t* status, moa_stream_t stream) {
   using namespace moa;
   MOA_REQUIRE(flags && status, "peer_barrier: null pointer");
   MOA_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "peer_barrier: 1..8 ranks");
@@ -106,7 +119,8 @@ int moa_peer_barrier(void* const* flags, int rank, int world, uint32_t epoch, in
   BarrierParams p;
   for (int g = 0; g < kMaxPeers; ++g) p.flags[g] = g < world ? reinterpret_cast<uint32_t*>(flags[g]) : nullptr;
   for (int g = 0; g < world; ++g) MOA_REQUIRE(p.flags[g] != nullptr, "peer_barrier: null flag pointer");
-  p.rank = rank; p.world = world; p.epoch = epoch; p.limit_cycles = (long long)limit_cycles; p.status = status;
+  p.rank = rank; p.world = world; p.epoch = epoch; p.epoch_counter = epoch_counter;
+  p.limit_cycles = (long long)limit_cycles; p.status = status;
   peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p);
   MOA_CUDA_CHECK(cudaGetLastError());
   return MOA_OK;

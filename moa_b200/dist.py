@@ -176,6 +176,10 @@ class PeerGather:
     ``k`` of call ``c + 2`` has passed the barrier of call ``c + 1``, which every other rank enters only after
     its ``o_proj`` of call ``c`` has read buffer ``k``.  Calls must be made by all ranks in the same order.
 
+    The barrier kernel numbers the calls itself (a counter in device memory), so a CUDA graph that contains an
+    even number of ``decode_and_gather`` calls (the buffer in turn is chosen on the host when the call is
+    captured) can be replayed, by every rank alike.
+
     The barrier's wait is bounded (``wait_seconds``); if a rank never arrives the others carry on with an
     incomplete buffer and ``check()`` raises.  ``close()`` unmaps and frees; call it on every rank before the
     process group is destroyed."""
@@ -216,6 +220,7 @@ class PeerGather:
                         for k in range(2)]
         self._flag_ptrs = (ctypes.c_void_p * G)(*[b + 2 * self.slot_bytes for b in self.bases])
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._calls = torch.zeros(1, dtype=torch.int32, device=self.device)    # the barrier kernel counts its calls here
         self.epoch = 0
         self.limit_cycles = int(min(2e10, max(1.0, wait_seconds) * 2.0e9))
         if G > 1:
@@ -237,7 +242,7 @@ class PeerGather:
         self.epoch += 1
         with torch.cuda.device(self.device):
             _lib.check("moa_peer_barrier", _lib.lib.moa_peer_barrier(
-                self._flag_ptrs, self.sh.rank, self.sh.world_size, self.epoch & 0xFFFFFFFF, self.limit_cycles,
+                self._flag_ptrs, self.sh.rank, self.sh.world_size, 0, self._calls.data_ptr(), self.limit_cycles,
                 self.status.data_ptr(), _lib.current_stream(self.device)))
         return full
 

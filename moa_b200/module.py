@@ -408,6 +408,60 @@ class MoALlamaForCausalLM(nn.Module):
         return self.lm_head(hidden), cache
 
 
+class DecodeGraph:
+    """One decode step of the whole model (every layer's projection GEMMs, fused decode launch, gather,
+    ``o_proj``, MLP, and ``lm_head`` for a causal LM) captured once in a CUDA graph and replayed per token.
+
+    Not in the reference, which launches every kernel of every layer from Python on each step; at decode batch
+    sizes the GPU work of a layer is tens of microseconds and the launches dominate.  What has to live on the
+    device for a replay to be exact does: the position (a device counter that the graph itself advances and the
+    rotary tables are computed from), the ring write pointers and lengths (advanced by the decode kernel), and
+    the call number of the cross-rank barrier.  The layer's token count is passed to the decode kernel by
+    value, which is exact once every ring has left its static part — capture is refused before that.
+
+    Use: run the prefill and one ordinary decode step (libraries initialise lazily on the first one), then::
+
+        graph = DecodeGraph(model, cache)          # model: MoALlamaModel or MoALlamaForCausalLM
+        out = graph.step(next_ids)                 # (B, 1, hidden) or (B, 1, vocab); overwritten by the next step
+
+    With sharded heads every rank must capture and replay alike; a ``PeerGather`` needs an even number of
+    layers (its two buffers alternate by call)."""
+
+    def __init__(self, model, cache: StaticCircularCache):
+        self.model = model
+        self.cache = cache
+        base = model.model if isinstance(model, MoALlamaForCausalLM) else model
+        device, B = base.device, cache.batch_size
+        for layer in range(cache.num_layers):
+            if cache.get_seq_length(layer) <= max(cache._static_host[layer]):
+                raise RuntimeError("DecodeGraph: capture once every ring has left its static part "
+                                   "(the prompt plus the tokens decoded so far must exceed the sink size)")
+        if any(l.self_attn.peer_gather is not None for l in base.layers) and len(base.layers) % 2:
+            raise RuntimeError("DecodeGraph: the fused gather alternates two buffers by call and needs an even "
+                               "number of layers per captured step")
+        self.ids = torch.zeros(B, 1, dtype=torch.long, device=device)
+        self.position = torch.full((1, 1), cache.get_seq_length(), dtype=torch.long, device=device)
+        kv_len, cache_position = list(cache._kv_len), cache.cache_position
+        stream = torch.cuda.Stream(device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=stream):
+            out, _ = model(self.ids, past_key_values=cache, position_ids=self.position)
+            self.position.add_(1)
+            self.out = out
+        torch.cuda.current_stream(device).wait_stream(stream)
+        # capturing ran the host side once without executing anything: take the host counters back
+        cache._kv_len, cache.cache_position = kv_len, cache_position
+
+    @torch.no_grad()
+    def step(self, input_ids: Tensor) -> Tensor:
+        self.ids.copy_(input_ids, non_blocking=True)
+        self.graph.replay()
+        self.cache._kv_len = [n + 1 for n in self.cache._kv_len]
+        self.cache.cache_position += 1
+        return self.out
+
+
 class _ModelHolder:
     """``model.model`` indirection of HuggingFace causal-LM wrappers, for a bare ``MoALlamaModel``."""
 

@@ -344,3 +344,37 @@ def test_head_sharded_model_on_one_gpu_equals_unsharded():
         for i, (g, w) in enumerate(zip(got[rank], want)):
             a, r = _rel(g, w)
             assert a < 2e-2 and r < 1e-2, (rank, i, a, r)
+
+
+def test_decode_graph_replays_are_identical_to_eager_steps():
+    """A whole-model decode step captured in a CUDA graph and replayed, against the same steps launched one by
+    one on an identical model: outputs and the ring state must be the same bit for bit, across a ring's wrap."""
+    plan = {"alphas": [[128.0, 128.0, 256.0, 1024.0], [256.0, 128.0, 64.0, 2048.0]],
+            "betas": [[0.0, 0.0, 0.0, 0.5], [0.0, 0.0, 0.25, 0.0]]}
+    ids = torch.randint(0, 100, (2, 300), device="cuda")
+    nxt = [torch.randint(0, 100, (2, 1), device="cuda") for _ in range(80)]
+    m1, m2 = _tiny_model(7), _tiny_model(7)
+    for m in (m1, m2):
+        m.set_mixture_of_attention(plan, moa_max_new_token=64)
+    h1, c1 = m1(ids)
+    h2, c2 = m2(ids)
+    h1, c1 = m1(nxt[0], past_key_values=c1)          # one ordinary decode step before capturing
+    h2, c2 = m2(nxt[0], past_key_values=c2)
+    assert torch.equal(h1, h2)
+    graph = moa_b200.DecodeGraph(m2, c2)
+    assert c2.get_seq_length() == 301                  # capturing did not advance the host counters
+    for t in nxt[1:]:
+        h1, c1 = m1(t, past_key_values=c1)
+        out = graph.step(t)
+        assert torch.equal(out, h1)
+    assert c2.get_seq_length() == c1.get_seq_length() == 380
+    for layer in range(2):
+        assert torch.equal(c1.cache_update_index[layer], c2.cache_update_index[layer])
+        assert torch.equal(c1.key_cache[layer], c2.key_cache[layer])
+        assert torch.equal(c1.cache_valid_length[layer], c2.cache_valid_length[layer])
+    # a cache whose rings are still in their static part is refused
+    m3 = _tiny_model(7)
+    m3.set_mixture_of_attention(plan, moa_max_new_token=64)
+    _, c3 = m3(ids[:, :40])
+    with pytest.raises(RuntimeError, match="static part"):
+        moa_b200.DecodeGraph(m3, c3)

@@ -105,7 +105,14 @@ def _worker(rank, world, port, ret):
             a, ca = ref_m(t, past_key_values=ca)
             b, cb = sh_m(t, past_key_values=cb)
             worst_model = max(worst_model, rel(b, a))
+        # the same steps from a CUDA graph (fused gather inside; the barrier kernel counts its calls on the device)
+        graph = moa_b200.DecodeGraph(sh_m, cb)
+        for t in [torch.randint(0, 100, (2, 1), generator=gen2).to(dev) for _ in range(6)]:
+            a, ca = ref_m(t, past_key_values=ca)
+            b = graph.step(t)
+            worst_model = max(worst_model, rel(b, a))
         pg.check()
+        del graph
         pg.close()
         assert worst_model < 1e-2, worst_model
         ret[rank] = worst
@@ -163,14 +170,19 @@ def test_peer_barrier_gives_up_when_a_rank_never_arrives():
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     ptrs = (ctypes.c_void_p * 2)(flags0.data_ptr(), flags1.data_ptr())
     stream = torch.cuda.current_stream().cuda_stream
-    assert lib.moa_peer_barrier(ptrs, 0, 2, 1, 20_000_000, status.data_ptr(), stream) == 0
+    assert lib.moa_peer_barrier(ptrs, 0, 2, 1, 0, 20_000_000, status.data_ptr(), stream) == 0
     torch.cuda.synchronize()
     assert status.tolist() == [21, 1, 1, 0]
     assert flags0.tolist()[:2] == [1, 0] and flags1.tolist()[0] == 1      # rank 0 published its arrival to both
     # a barrier whose partner has arrived (the word is already there) passes and leaves the status alone
     status.zero_()
     flags0[1] = 2
-    assert lib.moa_peer_barrier(ptrs, 0, 2, 2, 20_000_000, status.data_ptr(), stream) == 0
+    assert lib.moa_peer_barrier(ptrs, 0, 2, 2, 0, 20_000_000, status.data_ptr(), stream) == 0
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
-    assert lib.moa_peer_barrier(ptrs, 0, 9, 3, 1000, status.data_ptr(), stream) == 1       # more than 8 ranks: refused
+    # the call number counted on the device: the third call waits for 3, which the partner has not published
+    calls = torch.full((1,), 2, dtype=torch.int32, device="cuda")
+    assert lib.moa_peer_barrier(ptrs, 0, 2, 0, calls.data_ptr(), 20_000_000, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert calls.item() == 3 and status.tolist() == [21, 1, 3, 0] and flags1.tolist()[0] == 3
+    assert lib.moa_peer_barrier(ptrs, 0, 9, 3, 0, 1000, status.data_ptr(), stream) == 1    # more than 8 ranks: refused
