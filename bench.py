@@ -58,11 +58,12 @@ FALLBACK_BF16_TFLOPS = 1590.0
 MIN_BLOCKS = 25            # repeats of the K-step block
 MIN_REGION_S = 0.25        # GPU time the repeated blocks should add up to
 # DRAM traffic per launch is not measured by this program: it is scaled from one ncu capture of the same
-# kernel on a smaller case (decode: batch 4; prefill: N = 16384), where dram__bytes_read.sum +
-# dram__bytes_write.sum came to these multiples of the algorithmic bytes; traffic grows in proportion to
-# the rows streamed (decode) and to the tensor sizes (prefill: Q, K, V read once, O written once).
+# kernel on a smaller case (decode: batch 4; prefill: N = 32768, the smallest size that runs in the same kernel
+# form as config 3), where dram__bytes_read.sum + dram__bytes_write.sum came to these multiples of the
+# algorithmic bytes; traffic grows in proportion to the rows streamed (decode) and to the tensor sizes
+# (prefill: Q, K, V read once, O written once).
 DECODE_DRAM_TRAFFIC_RATIO = 1.027
-PREFILL_DRAM_TRAFFIC_RATIO = 0.967
+PREFILL_DRAM_TRAFFIC_RATIO = 0.986
 
 
 def config1_caps(seed: int):
@@ -370,9 +371,13 @@ def prefill_config3_leg(device, dist, world, rank, peaks_tf, which, N=65536, e2e
                "tflops_mean_of_launches": flops / (ms_mean * 1e-3) / 1e12,
                "shard_imbalance": max(loads) / (sum(loads) / len(loads)),
                "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks_tf, "unit": "TFLOP/s",
-                            "frac": tf / world / peaks_tf, "peak_source": which, "per": "GPU",
-                            "traffic": PREFILL_DRAM_TRAFFIC_RATIO * 4 * Hl * N * D * 2,
-                            "traffic_source": "ncu at N = 16384, scaled by the tensor sizes"}}
+                            "frac": tf / world / peaks_tf, "peak_source": which, "per": "GPU"}}
+        if 2 * Hl * N * D * 2 > (384 << 20):       # the kernel form that was captured (one block per unit)
+            res["roofline"].update(traffic=PREFILL_DRAM_TRAFFIC_RATIO * 4 * Hl * N * D * 2,
+                                   traffic_source="ncu at N = 32768 (same kernel form), scaled by the tensor sizes")
+        else:
+            res["roofline"].update(traffic=None, traffic_source="no capture of the persistent form at this shape (at 32 "
+                                   "heads x 16384 tokens it read 2.5 x the tensors' bytes: chunked unit order)")
         if world > 1:
             # whole-layer variant: gather the ranks' outputs (bandwidth-bound: 512/G MiB per rank)
             full = torch.empty(world, 1, N, Hl, D, dtype=torch.bfloat16, device=device)
@@ -456,9 +461,8 @@ def prefill_config0_leg(device, peaks_tf, which, cpu=True):
                "timing": "median of 20 single launches, each enqueued behind a 256 MB fill that flushes L2",
                "ms_back_to_back_l2_warm": warm_ms, "tflops_back_to_back_l2_warm": flops / (warm_ms * 1e-3) / 1e12,
                "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks_tf, "unit": "TFLOP/s",
-                            "frac": tf / peaks_tf, "peak_source": which,
-                            "traffic": PREFILL_DRAM_TRAFFIC_RATIO * 4 * Hp * N * D * 2,
-                            "traffic_source": "ncu at N = 16384, scaled by the tensor sizes"}}
+                            "frac": tf / peaks_tf, "peak_source": which, "traffic": None,
+                            "traffic_source": "not captured at this size (Q, K, V and O, 64 MB, fit in L2)"}}
         hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
         ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
 

@@ -12,9 +12,7 @@ The step after attention, ``o_proj`` (``MoA/models/llama/modeling_llama.py:329-3
 comes in two forms here: the gathered one (all-gather the head shards, then the full projection on every
 rank, as the reference's single-GPU code computes it) and a row-parallel one (every rank multiplies its
 heads by its column block of the weight and the partial results are summed with an all-reduce), which
-moves ``1/G`` of the weight per rank instead of all of it.  The all-gather can also be started without
-waiting for it (``all_gather_start`` / ``all_gather_finish``), so that a second micro-batch's attention
-runs while the first one's shards are in flight.
+moves ``1/G`` of the weight per rank instead of all of it.
 """
 from __future__ import annotations
 
@@ -96,30 +94,6 @@ class HeadSharding:
             self._gather_buffers[key] = buf
         with _lib.nvtx_range("moa_b200.all_gather"):
             dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)   # rank r fills rows [r*B, (r+1)*B)
-        return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
-
-    def all_gather_start(self, local: Tensor, slot: int = 0):
-        """Starts the all-gather of ``(B, q, H/G, D)`` on the communication stream and returns a handle;
-        work issued before ``all_gather_finish(handle)`` overlaps the transfer.  ``slot`` picks one of
-        several cached buffers, one per gather that is in flight at the same time."""
-        B, q, Hl, D = local.shape
-        if self.world_size == 1:
-            return (None, local, (B, q, Hl, D))
-        key = (local.device, local.dtype, B, q, Hl, D, "async", slot)
-        buf = self._gather_buffers.get(key)
-        if buf is None:
-            buf = torch.empty(self.world_size * B, q, Hl, D, dtype=local.dtype, device=local.device)
-            self._gather_buffers[key] = buf
-        work = dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group, async_op=True)
-        return (work, buf, (B, q, Hl, D))
-
-    def all_gather_finish(self, handle) -> Tensor:
-        """Makes the current stream wait for a gather started with ``all_gather_start`` and returns
-        ``(B, q, H, D)`` in ``order``."""
-        work, buf, (B, q, Hl, D) = handle
-        if work is None:
-            return buf
-        work.wait()
         return buf.view(self.world_size, B, q, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, q, self.world_size * Hl, D)
 
     def local_output_columns(self, w_o: Tensor, head_dim: int) -> Tensor:

@@ -52,9 +52,6 @@ def _worker(rank, world, port, caps, ret):
         assert torch.equal(gathered[:, :, rank * len(mine):(rank + 1) * len(mine)], out_loc)
         restored = sh.unpermute(gathered)
         err = float((restored - full).abs().max())
-        # the gather started without waiting gives the same tensor
-        again = sh.all_gather_finish(sh.all_gather_start(out_loc))
-        assert torch.equal(again, gathered)
         # o_proj after attention: gathered form and row-parallel form against the unsharded product.
         # The weight's columns follow the head order, so they are permuted into shard order first.
         from moa_b200 import permute_output_projection

@@ -47,8 +47,6 @@ def _worker(rank, world, port, ret):
             gathered = sh.all_gather(out)
             got = sh.unpermute(gathered)
             worst = max(worst, float((got.float() - ref.float()).abs().max()))
-            # the asynchronous gather returns the same tensor
-            assert torch.equal(sh.all_gather_finish(sh.all_gather_start(out)), gathered)
             # o_proj: gathered and row-parallel forms against the projection of the single-GPU output
             w = (torch.randn(256, H * D, generator=gen) * 0.05).half().to(dev)       # columns in head order
             w_perm = w.view(256, H, D)[:, sh.order].reshape(256, H * D).contiguous()
