@@ -541,8 +541,13 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
     gathered = sh.all_gather(out).clone()
     pg = None
     fused_equal = None
+    peer_error = None
     if world > 1:
-        pg = moa_b200.PeerGather(sh, Bl, Dl, torch.bfloat16, device)
+        try:        # set-up fails on all ranks alike or on none (PeerGather agrees on the outcome first)
+            pg = moa_b200.PeerGather(sh, Bl, Dl, torch.bfloat16, device)
+        except Exception as exc:
+            peer_error = f"{type(exc).__name__}: {exc}"[:300]
+    if pg is not None:
         fill_rings_directly(cache, 0, device, mine_ids, 131072, 4000)
         fused = pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
         pg.check()
@@ -619,7 +624,8 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
                         f"U[1k,16k] + 64 sinks, heads sharded over {world} GPU(s)", "us_per_step": us,
             "tokens_per_s": Bl / (us * 1e-6), "aggregate_hbm_gbs": kv_bytes_all / (us * 1e-6) / 1e9,
             "gather": "decode kernel stores its rows into every rank's buffer over NVLink + barrier kernel" if pg is not None
-                      else "none (one GPU)",
+                      else ("none (one GPU)" if world == 1 else f"NCCL all-gather + copy (peer buffers unavailable: {peer_error})"),
+            "extrapolated_80_layers_ms": us * 80 / 1e3,
             "breakdown_us": {"attention_kernel": res["attention_only_us"],
                              "peer_store_gather_and_barrier": us - res["attention_only_us"],
                              "nccl_allgather_and_copy": us_nccl - res["attention_only_us"]},
@@ -676,7 +682,11 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     per_step_eager = per_step_nccl = statistics.median(ms) / steps
     pg = None
     if world > 1:        # the same steps with the gather done by the decode kernel (peer stores + barrier kernel)
-        pg = model.model.enable_peer_gather(batch)
+        try:             # set-up fails on all ranks alike or on none
+            pg = model.model.enable_peer_gather(batch)
+        except Exception:
+            pg = None
+    if pg is not None:
         for i in range(warmup):
             step(i)
         ms, _ = time_blocks(step, steps, device, dist, min_blocks=3, min_region_s=0.2)
@@ -700,8 +710,8 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
                         f"{layers} layers, heads sharded over {world} GPU(s)",
             "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
-            "how": "one CUDA graph per decode step (all layers), gather by the decode kernel's peer stores" if world > 1
-                   else "one CUDA graph per decode step (all layers)",
+            "how": "one CUDA graph per decode step (all layers)" + (", gather by the decode kernel's peer stores"
+                   if pg is not None else (", NCCL all-gather" if world > 1 else "")),
             "ms_per_step_eager_launches": per_step_eager,
             "ms_per_step_eager_nccl_allgather": per_step_nccl if world > 1 else None,
             "kv_bytes_per_step_per_gpu": kv_bytes, "weight_bytes_per_step_per_gpu": weights,
@@ -847,7 +857,12 @@ def run_gpu(args):
             prefill0 = prefill_config0_leg(device, tf_peak, which, cpu=not args.no_cpu_baseline)
     del cache, pool
     torch.cuda.empty_cache()
-    layer = layer_leg(device, dist, world, rank) if not args.no_layer else None
+    layer = None
+    if not args.no_layer:
+        try:
+            layer = layer_leg(device, dist, world, rank)
+        except Exception as exc:      # the decode headline must still be reported
+            layer = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     line = None
     if rank == 0:

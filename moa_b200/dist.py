@@ -172,23 +172,51 @@ class PeerGather:
         self.slot_bytes = (payload + 255) // 256 * 256
         total = 2 * self.slot_bytes + 256
         lib = _lib.lib
+        self._own = None
+        self.bases: List[int] = []
+        failure: Optional[Exception] = None
         with torch.cuda.device(self.device):
+            # Set-up is collective: every step is attempted on every rank and the outcome is agreed on before
+            # anybody raises, so that a rank whose mapping failed cannot leave the others waiting in a collective.
             base = ctypes.c_void_p()
-            _lib.check("moa_peer_alloc", lib.moa_peer_alloc(ctypes.byref(base), total))
             handle = ctypes.create_string_buffer(64)
-            _lib.check("moa_peer_export", lib.moa_peer_export(base, handle))
+            try:
+                _lib.check("moa_peer_alloc", lib.moa_peer_alloc(ctypes.byref(base), total))
+                self._own = base.value
+                _lib.check("moa_peer_export", lib.moa_peer_export(base, handle))
+            except Exception as exc:
+                failure = exc
             handles: List[Optional[bytes]] = [None] * G
             if G > 1:
-                dist.all_gather_object(handles, handle.raw, group=sharding.group)
-            self.bases: List[int] = []
-            for g in range(G):
-                if g == sharding.rank:
-                    self.bases.append(base.value)
-                else:
-                    p = ctypes.c_void_p()
-                    _lib.check("moa_peer_open", lib.moa_peer_open(handles[g], ctypes.byref(p)))
-                    self.bases.append(p.value)
-        self._own = base.value
+                dist.all_gather_object(handles, handle.raw if failure is None else None, group=sharding.group)
+            if failure is None and any(h is None for g, h in enumerate(handles) if g != sharding.rank):
+                failure = RuntimeError("PeerGather: another rank could not allocate or export its buffer")
+            if failure is None:
+                try:
+                    for g in range(G):
+                        if g == sharding.rank:
+                            self.bases.append(base.value)
+                        else:
+                            p = ctypes.c_void_p()
+                            _lib.check("moa_peer_open", lib.moa_peer_open(handles[g], ctypes.byref(p)))
+                            self.bases.append(p.value)
+                except Exception as exc:
+                    failure = exc
+            if G > 1:
+                verdict: List[Optional[bool]] = [None] * G
+                dist.all_gather_object(verdict, failure is None, group=sharding.group)
+                if failure is None and not all(verdict):
+                    failure = RuntimeError("PeerGather: another rank could not map the buffers (CUDA IPC between "
+                                           f"the ranks' GPUs is needed); ranks that failed: "
+                                           f"{[g for g, ok in enumerate(verdict) if not ok]}")
+            if failure is not None:
+                for g, b in enumerate(self.bases):
+                    if g != sharding.rank:
+                        lib.moa_peer_close(b)
+                if self._own is not None:
+                    lib.moa_peer_free(self._own)
+                    self._own = None
+                raise failure
         raw = torch.as_tensor(_RawDeviceMemory(base.value, total), device=self.device)
         self.buffers = [raw[k * self.slot_bytes:k * self.slot_bytes + payload].view(dtype).view(batch_size, 1, self.H, head_dim)
                         for k in range(2)]
