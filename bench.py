@@ -718,6 +718,49 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
             "hbm_gbs_per_gpu": (kv_bytes + weights) / (per_step * 1e-3) / 1e9}
 
 
+def model_prefill_leg(device, n_tokens: int = 65536, layers: int = 32):
+    """Config 3 of BASELINE.json as a whole model: Llama-3-8B architecture converted to MHA (32 layers, 32 heads x
+    128, hidden 4096, FFN 14336, rope_theta 5e5, bf16), random-init weights, one 65536-token random-token
+    sequence, per-head plan alpha in {512..4096}, beta in [0, 0.3), 64 sinks.  One forward = per layer the fused
+    QKV GEMM, the rotary embedding of q and k in place, the ring-cache fill, the block-sparse prefill kernel (all
+    reading the GEMM's output through strides), o_proj and the MLP; GEMMs and norms are library kernels."""
+    import moa_b200
+
+    hidden, heads, ffn = 4096, 32, 14336
+    rng = np.random.RandomState(3000)
+    plan = {"alphas": [[float(rng.choice([512, 1024, 2048, 4096])) for _ in range(heads)] for _ in range(layers)],
+            "betas": [[float(rng.uniform(0, 0.3)) for _ in range(heads)] for _ in range(layers)]}
+    model = moa_b200.MoALlamaForCausalLM(layers, hidden, heads, ffn, vocab_size=32000, rope_theta=500000.0,
+                                         dtype=torch.bfloat16, device=device, rms_norm_eps=1e-5)
+    gen = torch.Generator(device=device).manual_seed(3000)
+    for prm in model.parameters():
+        if prm.dim() > 1:
+            prm.data.normal_(0, 0.02, generator=gen)
+    model.set_mixture_of_attention(plan, permute_head=True, moa_max_new_token=0)
+    ids = torch.randint(0, 32000, (1, n_tokens), device=device, generator=gen)
+    cfg = moa_b200.moa_config_to_cache_config(model.model.moa_config, n_tokens, 0, verbose=False)
+    attn_flops = sum(moa_b200.prefill_flops(1, n_tokens, 128, [s // 64 for s in st], [(c - s) // 64 for c, s in zip(cs, st)])
+                     for cs, st in zip(cfg["cache_size"], cfg["static_size"]))
+    gemm_flops = layers * 2 * n_tokens * (hidden * 3 * hidden + hidden * hidden + 3 * hidden * ffn)
+    times = []
+    for i in range(3):
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits, cache = model(ids)
+        e1.record()
+        torch.cuda.synchronize(device)
+        times.append(e0.elapsed_time(e1))
+        del cache
+    ms = min(times[1:])
+    return {"workload": f"config3 whole model: Llama-3-8B-as-MHA architecture, random weights, prefill of {n_tokens} tokens, "
+                        f"{layers} layers, bf16, 1 GPU", "ms": ms, "tokens_per_s": n_tokens / (ms * 1e-3),
+            "attention_tflop": attn_flops / 1e12, "gemm_tflop": gemm_flops / 1e12,
+            "tflops_total": (attn_flops + gemm_flops) / (ms * 1e-3) / 1e12,
+            "timing": "best of 2 forwards after one warm-up, CUDA events, ring caches built and filled inside",
+            "logits_finite": bool(torch.isfinite(logits.float()).all())}
+
+
 def run_gpu(args):
     import moa_b200
 
@@ -753,6 +796,8 @@ def run_gpu(args):
     if args.leg == "model":
         return finish({"model": model_leg(device, dist, world, rank, steps=max(1, min(args.steps, 16)),
                                           layers=args.model_layers)})
+    if args.leg == "model-prefill":
+        return finish({"model_prefill": model_prefill_leg(device, args.prefill_n, args.model_layers)} if rank == 0 else None)
     if args.leg == "layer":
         return finish({"layer_allgather": layer_leg(device, dist, world, rank)})
 
@@ -921,9 +966,10 @@ def main():
     ap.add_argument("--impl", default="moa_b200", choices=["moa_b200", "reference"])
     ap.add_argument("--batch", type=int, default=16, help="batch size (16 = config 1; smaller only for profiler captures)")
     ap.add_argument("--fill-tokens", type=int, default=PREFILL_TOKENS, help="tokens the caches are filled from")
-    ap.add_argument("--leg", default="all", choices=["all", "prefill", "model", "layer"],
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "model", "model-prefill", "layer"],
                     help="'prefill': only the prefill legs; 'model': whole-model decode of config 2 (heads sharded over "
-                         "the GPUs); 'layer': only the config-4 attention layer with its gather")
+                         "the GPUs); 'model-prefill': whole-model prefill of config 3 (one GPU); 'layer': only the "
+                         "config-4 attention layer with its gather")
     ap.add_argument("--prefill-n", type=int, default=65536, help="sequence length of the config-3 prefill leg")
     ap.add_argument("--model-layers", type=int, default=32, help="layers of the config-2 model leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill legs")
