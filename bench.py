@@ -26,7 +26,7 @@ Further legs on the same line (each with its own roofline): `prefill` — the bl
 on one layer of config 3 (B1 H32 N65536 D128 bf16), its 32 heads sharded over the N GPUs, and on config 0
 (B1 H32 N2048 fp16) on one GPU; `layer_allgather` — one decode layer of config 4 (64 heads, batch 64,
 bf16) with its heads sharded over the N GPUs and the outputs gathered before o_proj (strong scaling);
-`--leg model` — whole-model decode of config 2 with its heads sharded over the N GPUs.
+`model_config2` (alone: `--leg model`) — whole-model decode of config 2 with its heads sharded over the N GPUs.
 
 `--impl reference` times the CPU restatement of the reference's own path (ring update + grouped SDPA,
 the oracle under oracle/) on the host cores, on the same config.
@@ -909,6 +909,14 @@ def run_gpu(args):
         except Exception as exc:      # the decode headline must still be reported
             layer = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
+    model = None
+    if not args.no_model:
+        torch.cuda.empty_cache()
+        try:
+            model = model_leg(device, dist, world, rank, steps=8, layers=args.model_layers)
+        except Exception as exc:      # the decode headline must still be reported
+            model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     line = None
     if rank == 0:
         st = block_stats(ms_blocks, steps)
@@ -950,6 +958,8 @@ def run_gpu(args):
             line["prefill_config0"] = prefill0
         if layer is not None:
             line["layer_allgather"] = layer
+        if model is not None:
+            line["model_config2"] = model
         if world == 1 and not args.no_cpu_baseline:
             val, per_step, cores = cpu_decode_tok_per_s(caps, 30, 1000)
             line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
@@ -974,6 +984,7 @@ def main():
     ap.add_argument("--model-layers", type=int, default=32, help="layers of the config-2 model leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill legs")
     ap.add_argument("--no-layer", action="store_true", help="skip the config-4 layer leg")
+    ap.add_argument("--no-model", action="store_true", help="skip the config-2 whole-model decode leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host timing of the prefill leg")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline legs")
     args = ap.parse_args()
