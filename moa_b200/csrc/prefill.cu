@@ -1,17 +1,19 @@
 // Block-sparse causal prefill (attention sink + per-head sliding window) on tcgen05 / TMEM / TMA.
 //
-// A persistent kernel: one thread block per SM, each working through 256-row query super-tiles of one
-// (batch, head) handed out by an atomic counter, heaviest first.  A super-tile is two 128-row tiles A and B
-// that share every K/V tile brought into shared memory.  Roles:
+// The unit of work is a 256-row query super-tile of one (batch, head): two 128-row tiles A and B that share
+// every K/V tile brought into shared memory.  The kernel comes in two forms (a template flag; the launcher
+// chooses by shape): persistent — one thread block per SM working through units handed out by an atomic
+// counter, heaviest first — and one block per unit.  Roles of a block:
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread r owns query row r of its
 //              tile (= TMEM lane r).  Per KV block it loads its S row from TMEM, computes the
 //              exponentials against a lazily updated max, writes P (fp16/bf16, two per 32-bit
 //              column) over the first half of the S buffer the row came from, rescales O in TMEM
 //              when the max moved, and finally runs the epilogue
 //   warp  8    scheduler + TMA producer (one lane): fetches the next super-tile, publishes it to the other
-//              roles through a two-entry ring, loads both Q tiles, then K and V tiles of 64 tokens through
-//              two rings of shared-memory stages.  It runs ahead of the others: the next super-tile's Q and
-//              first K/V tiles arrive while the softmax warps are still in the epilogue of this one
+//              roles through a two-entry ring (persistent form), loads both Q tiles, then K and V tiles of 64
+//              tokens through two rings of shared-memory stages.  It runs ahead of the others: the next
+//              super-tile's Q and first K/V tiles arrive while the softmax warps are still in the epilogue of
+//              this one
 //   warp  9,10 MMA issuers of tile A and tile B (warp 9 owns the TMEM allocation):
 //              S = Q K^T (M128 N64 K128, Q and K from shared memory), O += P V (M128 N128 K64,
 //              P from TMEM, V from shared memory as an MN-major operand).  The whole warp runs the
@@ -1038,12 +1040,8 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   // chunk 2 +16 %, 16384 tokens (268 MB) chunk 4 +3 % and chunk 2 -1 %, 32768 tokens (537 MB) chunk 16 -2 %,
   // 65536 tokens chunk 16 -2 % and chunk 2 -11 %.
   const int64_t kv_bytes = (int64_t)B * H * N * D * 2 * 2;
-#ifdef MOA_PREFILL_CHUNK
-  p.chunk = (int)(MOA_PREFILL_CHUNK < 1 ? 1 : (MOA_PREFILL_CHUNK > nsuper ? nsuper : MOA_PREFILL_CHUNK));
-#else
   p.chunk = kv_bytes <= (96ll << 20) ? 1 : kv_bytes <= (192ll << 20) ? 2 : kv_bytes <= (384ll << 20) ? 4 : (int)nsuper;
   if (p.chunk > nsuper) p.chunk = (int)nsuper;
-#endif
   // one block per SM (shared memory and TMEM allow no more), fewer when there are fewer super-tiles
   int sms = 0;
   {
@@ -1063,11 +1061,7 @@ extern "C" int moa_prefill_fwd(const void* q, const void* k, const void* v, void
   // 16384: +5 % against one block per unit); beyond that one block per unit does (65536: +1 %), and so it does
   // when there are not even two units per SM (2048 tokens of 32 heads: +4 %; the launch then ends when the
   // heaviest unit does, whoever runs the rest).
-#ifdef MOA_PREFILL_PERSISTENT
-  const bool persistent = MOA_PREFILL_PERSISTENT != 0;
-#else
   const bool persistent = kv_bytes <= (384ll << 20) && p.num_tiles > 2 * sms;
-#endif
   dim3 grid((unsigned)(persistent && sms < p.num_tiles ? sms : p.num_tiles));
   cudaStream_t st = (cudaStream_t)stream;
   const int variant = (persistent ? 8 : 0) + (dtype == MOA_BF16 ? 4 : 0) + (out_f32 ? 2 : 0) + (D == 64 ? 1 : 0);

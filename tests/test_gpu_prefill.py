@@ -325,3 +325,53 @@ def test_poisoned_rows_past_the_sequence_and_guard_rows(N):
     assert torch.isfinite(out.float()).all(), "rows past the sequence end were read"
     _close(out, ref, f"poisoned tail, N={N}")
     assert (outbuf[:, :64] == marker).all() and (outbuf[:, 64 + N:] == marker).all(), "rows outside the output were written"
+
+
+def test_persistent_form_ragged_many_units_against_oracle():
+    """480 units on 148 SMs: the launcher picks the persistent form (blocks take unit after unit from the counter).
+    Ragged length (the last super-tile has one tile of 88 rows), two batch rows, 80 heads whose plans cycle through
+    wide, narrow, sink-less and all-invisible spans: every role sees units with nothing to do next to full ones.
+    Whole output against the fp32 oracle; a second launch on the same buffers must give the same bits (the
+    scheduler words were put back to zero)."""
+    gen = torch.Generator().manual_seed(77)
+    B, H, N = 2, 80, 600
+    sink_b = [(1, 1, 0, 2, 0)[h % 5] for h in range(H)]
+    local_b = [(10, 1, 3, 2, 0)[h % 5] for h in range(H)]
+    q, k, v = (torch.randn(B, H, N, 128, generator=gen).half() for _ in range(3))
+    sm = 128 ** -0.5
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    sb, lb = (torch.tensor(x, dtype=torch.int32).cuda() for x in (sink_b, local_b))
+    out = moa_b200.sparse_prefill(qd, kd, vd, sm, sb, lb)
+    again = moa_b200.sparse_prefill(qd, kd, vd, sm, sb, lb)
+    moa_b200.check_device_status()
+    assert torch.equal(out, again)
+    _close(out, orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b), "persistent form, ragged, 480 units")
+    from moa_b200.attention import _status_words
+    assert _status_words("cuda:0").tolist() == [0] * 8
+
+
+def test_prefill_launches_on_two_streams_do_not_share_scheduler_state():
+    """Two persistent-form launches that overlap in time (two streams) each own a status buffer; results equal the
+    launches run one after the other."""
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    shapes = [(1, 48, 2048), (1, 40, 2304)]
+    data = []
+    for B, H, N in shapes:
+        q, k, v = (torch.randn(B, H, N, 128, generator=gen, device="cuda").half() for _ in range(3))
+        sb = torch.ones(H, dtype=torch.int32, device="cuda")
+        lb = torch.tensor([1 + (3 * h) % 20 for h in range(H)], dtype=torch.int32, device="cuda")
+        data.append((q, k, v, sb, lb))
+    want = [moa_b200.sparse_prefill(q, k, v, 0.09, sb, lb) for q, k, v, sb, lb in data]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for rnd in range(3):
+        got = []
+        for s, (q, k, v, sb, lb) in zip(streams, data):
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                got.append(moa_b200.sparse_prefill(q, k, v, 0.09, sb, lb))
+        for s in streams:
+            torch.cuda.current_stream().wait_stream(s)
+        moa_b200.check_device_status()
+        for g, w in zip(got, want):
+            assert torch.equal(g, w)
