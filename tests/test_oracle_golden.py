@@ -135,3 +135,16 @@ def test_decode_matches_reference_sdpa_path():
         assert (grp.float() - ref).abs().max() < 1e-3
     assert np.array_equal(cache.key_cache[0], g["key_cache_final"])
     assert np.array_equal(cache.cache_update_index[0], g["update_index_final"])
+
+
+def test_masked_sdpa_route_equals_the_fp32_oracle():
+    """The timed CPU baseline of the prefill (one scaled_dot_product_attention call with the boolean mask that
+    ``prefill_mask`` builds, which the layout fixtures above pin) gives the oracle's result."""
+    import torch
+    gen = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, 4, 300, 64, generator=gen) for _ in range(3))
+    sink_b, local_b = [1, 1, 0, 2], [1, 2, 3, 8]
+    a = orc.prefill_attention_masked_sdpa(q, k, v, 0.11, sink_b, local_b)
+    b = orc.prefill_attention_fp32(q, k, v, 0.11, sink_b, local_b)
+    assert a.shape == b.shape == (2, 300, 4, 64)
+    assert (a - b).abs().max().item() < 2e-5
