@@ -375,3 +375,21 @@ def test_prefill_launches_on_two_streams_do_not_share_scheduler_state():
         moa_b200.check_device_status()
         for g, w in zip(got, want):
             assert torch.equal(g, w)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_dim_64_persistent_form(dtype):
+    """64-wide heads with enough units (384 on 148 SMs) for the launcher to pick the persistent form."""
+    gen = torch.Generator().manual_seed(640)
+    B, H, N = 2, 64, 700
+    q, k, v = (torch.randn(B, H, N, 64, generator=gen).to(dtype) for _ in range(3))
+    sm = 64 ** -0.5
+    sink_b = [(1, 0, 2)[h % 3] for h in range(H)]
+    local_b = [1 + (5 * h) % 11 for h in range(H)]
+    ref = orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b)
+    if dtype == torch.float16:
+        _close(_run(q, k, v, sm, sink_b, local_b), ref, "D=64 fp16, persistent form")
+    else:
+        out32 = _run(q, k, v, sm, sink_b, local_b, out_dtype=torch.float32)
+        _close(out32, ref, "D=64 bf16, fp32 store, persistent form", *BF16_F32_STORE)
+        assert torch.equal(_run(q, k, v, sm, sink_b, local_b).cpu(), out32.cpu().bfloat16())
