@@ -623,11 +623,12 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
     return {"workload": "config4 one layer, attention + gather of the head shards: B64 H64 D128 bf16, windows "
                         f"U[1k,16k] + 64 sinks, heads sharded over {world} GPU(s)", "us_per_step": us,
             "tokens_per_s": Bl / (us * 1e-6), "aggregate_hbm_gbs": kv_bytes_all / (us * 1e-6) / 1e9,
-            "gather": "decode kernel stores its rows into every rank's buffer over NVLink + barrier kernel" if pg is not None
+            "gather": "one launch: the decode kernel stores its rows into every rank's buffer over NVLink and its last block "
+                      "runs the cross-rank barrier" if pg is not None
                       else ("none (one GPU)" if world == 1 else f"NCCL all-gather + copy (peer buffers unavailable: {peer_error})"),
             "extrapolated_80_layers_ms": us * 80 / 1e3,
             "breakdown_us": {"attention_kernel": res["attention_only_us"],
-                             "peer_store_gather_and_barrier": us - res["attention_only_us"],
+                             "peer_stores_and_barrier_in_the_launch": us - res["attention_only_us"],
                              "nccl_allgather_and_copy": us_nccl - res["attention_only_us"]},
             "us_per_step_nccl_allgather": us_nccl,
             "fused_gather_equals_nccl_gather": fused_equal,
@@ -710,7 +711,7 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
                         f"{layers} layers, heads sharded over {world} GPU(s)",
             "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
-            "how": "one CUDA graph per decode step (all layers)" + (", gather by the decode kernel's peer stores"
+            "how": "one CUDA graph per decode step (all layers)" + (", gather and barrier inside the decode launch"
                    if pg is not None else (", NCCL all-gather" if world > 1 else "")),
             "ms_per_step_eager_launches": per_step_eager,
             "ms_per_step_eager_nccl_allgather": per_step_nccl if world > 1 else None,

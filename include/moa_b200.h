@@ -109,17 +109,25 @@ int moa_decode_rope_fwd(const void* q, void* k_cache, void* v_cache, const void*
 
 /* ------------------------------------------------------------------------------------------
  * moa_decode_gather_fwd: the decode step of a head shard that delivers its output rows to every GPU of
- * the node in the same launch.  Stands for the attention of LlamaMixtureAttention.forward
- * (MoA/models/llama/modeling_llama.py:315-326) on one rank plus the gather of the ranks' head shards into
- * (B, 1, H, D) that has to precede o_proj (:329-330) when heads are sharded; the reference itself is
- * single-GPU and has no such step.
+ * the node, and waits for the other GPUs' rows, in the same launch.  Stands for the attention of
+ * LlamaMixtureAttention.forward (MoA/models/llama/modeling_llama.py:315-326) on one rank plus the gather of
+ * the ranks' head shards into (B, 1, H, D) that has to precede o_proj (:329-330) when heads are sharded; the
+ * reference itself is single-GPU and has no such step.
  *   out_peers    host array of n_out_peers (0..8) device pointers: the same place (out plus this rank's head
- *                offset) in the other GPUs' gather buffers, mapped into this process (peer access or symmetric
- *                memory).  Every output row is stored to out and, with the same strides, to each of them
- *                (plain stores over NVLink; nothing is loaded from a peer).
+ *                offset) in the other GPUs' gather buffers, mapped into this process (moa_peer_open).  Every
+ *                output row is stored to out and, with the same strides, to each of them (plain stores over
+ *                NVLink; nothing is loaded from a peer).
  *   rope_cos/sin both NULL or both given (as moa_decode_rope_fwd).
- * The launch only writes; the caller must order the peers' reads after it (a barrier across the ranks
- * after the kernel, before o_proj).  Everything else as moa_decode_fwd.
+ *   barrier_flags, rank, world, epoch_counter, limit_cycles, barrier_status
+ *                the cross-rank barrier at the end of the launch, with the meaning they have in
+ *                moa_peer_barrier (flags: host array of `world` device pointers; epoch_counter: a device uint32
+ *                of this rank, zero at the start, required here): the block that writes the last output row of
+ *                the launch publishes the call number to every rank and waits, for at most limit_cycles, until
+ *                every rank has published it to this one.  When the kernel has finished, this rank's buffer
+ *                holds all ranks' rows of the call (or barrier_status says which rank did not arrive).
+ *                barrier_flags NULL: the launch only stores; the caller orders the peers' reads itself
+ *                (moa_peer_barrier after it).  The workspace is the one of moa_decode_fwd.
+ * Everything else as moa_decode_fwd.
  * ------------------------------------------------------------------------------------------ */
 int moa_decode_gather_fwd(const void* q, void* k_cache, void* v_cache, const void* k_new, const void* v_new,
                           void* out, int64_t q_batch_stride, int64_t q_head_stride, int64_t new_batch_stride,
@@ -128,6 +136,8 @@ int moa_decode_gather_fwd(const void* q, void* k_cache, void* v_cache, const voi
                           int64_t* mask_cache, const int64_t* static_size, int64_t kv_len,
                           int B, int H, int D, int64_t S, float sm_scale, int dtype, int out_f32,
                           const void* rope_cos, const void* rope_sin, void* const* out_peers, int n_out_peers,
+                          void* const* barrier_flags, int rank, int world, uint32_t* epoch_counter,
+                          int64_t limit_cycles, int32_t* barrier_status,
                           void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

@@ -54,7 +54,7 @@ def _load() -> ctypes.CDLL:
     decode_args = [P] * 6 + [I64] * 6 + [P] * 5 + [I64, I, I, I, I64, c_float, I, I]
     lib.moa_decode_fwd.argtypes = decode_args + [P, I64, I, P]
     lib.moa_decode_rope_fwd.argtypes = decode_args + [P, P, P, I64, I, P]
-    lib.moa_decode_gather_fwd.argtypes = decode_args + [P, P, P, I, P, I64, I, P]
+    lib.moa_decode_gather_fwd.argtypes = decode_args + [P, P, P, I, P, I, I, P, I64, P, P, I64, I, P]
     lib.moa_decode_fwd_static.argtypes = decode_args + [I, P]
     lib.moa_rope_qk.argtypes = [P, P, I64, I64, I64, P, P, I64, I64, I, I, I64, I, I, P]
     lib.moa_selftest_bounded_wait.argtypes = [P, I64, P]

@@ -244,7 +244,7 @@ class StaticCircularCache:
     def decode_attention(self, query_states: Tensor, key_states: Tensor, value_states: Tensor, layer_idx: int,
                          sm_scale: float, out: Optional[Tensor] = None,
                          rope: Optional[Tuple[Tensor, Tensor]] = None, out_dtype: Optional[torch.dtype] = None,
-                         out_peers: Optional[Sequence[int]] = None) -> Tensor:
+                         out_peers: Optional[Sequence[int]] = None, barrier: Optional[Tuple] = None) -> Tensor:
         """One decode step of one layer in one launch: append the new ``(B, H, 1, D)`` K/V rows at
         the ring's write index, attend over the cache including the new token, advance the
         bookkeeping.  Same result as ``update(...)`` followed by
@@ -258,7 +258,9 @@ class StaticCircularCache:
         ``query_states`` and ``key_states`` itself; they are then the raw projection outputs.
         ``out_dtype=torch.float32`` stores the fp32 result unrounded (parity checks of the bf16 path).
         ``out_peers``: device addresses of the same slice in other GPUs' gather buffers (mapped into
-        this process); every output row is also stored there, see ``HeadSharding.decode_and_gather``.
+        this process); every output row is also stored there.  ``barrier``: the arguments of the cross-rank
+        barrier that then ends the launch, ``(flag pointer array, rank, world, call-counter address, limit in
+        cycles, status address)``; both are what ``PeerGather.decode_and_gather`` passes.
 
         The ring's write rule depends on the layer's token count, which is passed to the kernel by
         value from the host counter ``_kv_len``: a CUDA graph captured over this call replays the
@@ -300,11 +302,13 @@ class StaticCircularCache:
             cos, sin = cos.reshape(B, D).contiguous(), sin.reshape(B, D).contiguous()
             assert cos.dtype == self.dtype and sin.dtype == self.dtype and cos.device == device
         with torch.cuda.device(device):
-            if out_peers:
-                peers = (ctypes.c_void_p * len(out_peers))(*[int(a) for a in out_peers])
+            if out_peers or barrier is not None:
+                n_peers = len(out_peers) if out_peers else 0
+                peers = (ctypes.c_void_p * max(n_peers, 1))(*[int(a) for a in (out_peers or [])])
+                bar = barrier if barrier is not None else (None, 0, 0, None, 0, None)
                 with _lib.nvtx_range("moa_b200.decode_gather"):
                     _lib.check("moa_decode_gather_fwd", lib.moa_decode_gather_fwd(
-                        *args, _lib.ptr(cos), _lib.ptr(sin), peers, len(out_peers), *tail))
+                        *args, _lib.ptr(cos), _lib.ptr(sin), peers, n_peers, *bar, *tail))
             elif rope is not None:
                 with _lib.nvtx_range("moa_b200.decode_rope_fused"):
                     _lib.check("moa_decode_rope_fwd", lib.moa_decode_rope_fwd(

@@ -67,8 +67,14 @@ struct DecodeParams {
   int B, H;
   int64_t S;
   float scale_log2;  // sm_scale * log2(e)
-  int* tickets;      // (B, H), zero between launches
+  int* tickets;      // (B, H), zero between launches; one more word behind them counts the rows written (barrier)
   float* partials;   // (B, nchunks + H, D + 4)
+  // cross-GPU barrier at the end of the launch (moa_decode_gather_fwd with flags given), else bar_world == 0:
+  uint32_t* bar_flags[kMaxOutPeers];  // bar_flags[g]: rank g's flag words (one per rank), mapped into this process
+  int bar_rank, bar_world;
+  uint32_t* bar_epoch;                // this rank's call counter in device memory
+  long long bar_limit;                // bound of the wait, in SM cycles
+  int32_t* bar_status;                // int32[4]: {21, rank waited for, call number, this rank} when the wait ran out
   int64_t slots_per_batch;
   int chunk;
 };
@@ -126,8 +132,55 @@ __device__ __forceinline__ void store_out(const DecodeParams& p, int b, int h, i
   }
 }
 
+// Every output row of a launch is written by exactly one block.  The block that writes the last of the B*H rows
+// tells every rank "this rank's rows of call n are stored" and waits (bounded) until every rank has told this
+// one the same: when the kernel has finished, this rank's gather buffer holds all ranks' rows.  Called by all
+// threads of a block that has written `rows_written` > 0 rows.
+__device__ __noinline__ void decode_peer_barrier(const DecodeParams* pp, int rows_written) {
+  const DecodeParams& p = *pp;
+  __shared__ uint32_t sm_epoch;
+  __shared__ int sm_is_last;
+  const int tid = threadIdx.x;
+  __syncthreads();                               // all of this block's row stores are issued
+  if (tid == 0) {
+    __threadfence_system();                      // this block's rows first
+    int* rows_done = p.tickets + (int64_t)p.B * p.H;
+    const int before = atomicAdd(rows_done, rows_written);
+    sm_is_last = (before + rows_written == p.B * p.H);
+    if (sm_is_last) {
+      __threadfence_system();                    // ... and everybody else's, whose counts this thread has seen
+      *rows_done = 0;                            // ready for the next launch
+      const uint32_t e = *p.bar_epoch + 1u;
+      *p.bar_epoch = e;
+      sm_epoch = e;
+    }
+  }
+  __syncthreads();
+  if (sm_is_last && tid < p.bar_world) {
+    const uint32_t epoch = sm_epoch;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.bar_flags[tid] + p.bar_rank), "r"(epoch) : "memory");
+    const uint32_t* mine = p.bar_flags[p.bar_rank] + tid;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if ((int32_t)(seen - epoch) >= 0) break;
+      if ((spin & 63u) == 0 && clock64() - t0 > p.bar_limit) {
+        if (atomicCAS(&p.bar_status[0], 0, 21) == 0) {
+          p.bar_status[1] = tid;
+          p.bar_status[2] = (int32_t)epoch;
+          p.bar_status[3] = p.bar_rank;
+        }
+        break;
+      }
+    }
+    __threadfence_system();
+  }
+}
+
 template <typename T, int D, bool OUT_F32>
-__global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const __grid_constant__ DecodeParams p) {
   constexpr int LPR = D / 8;    // lanes that share one cache row (16 bytes each)
   constexpr int RPI = 32 / LPR; // rows a warp covers with one load instruction
   constexpr int TILE = RPI * kTileIters;
@@ -154,11 +207,15 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
 
   // Heads without any rows (head_start[h] == head_start[h+1]) are nobody's chunk: the first block of the
   // batch row writes their (all-zero) output, so that every (b, h) row of `out` is defined.
+  int rows_written = 0;   // output rows this block has written (the same in all threads)
   if (c == 0) {
     for (int h = 0; h < p.H; ++h) {
       const int64_t hs = hs_row[h];
       const int64_t he = (h + 1 < p.H) ? hs_row[h + 1] : p.S;
-      if (he <= hs && tid < D) store_out<T, OUT_F32>(p, b, h, tid, 0.f);
+      if (he <= hs) {
+        if (tid < D) store_out<T, OUT_F32>(p, b, h, tid, 0.f);
+        ++rows_written;
+      }
     }
   }
 
@@ -321,6 +378,7 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
       }
     }
     if (last) {
+      ++rows_written;
       if (tid < D) store_out<T, OUT_F32>(p, b, h, tid, (L > 0.f) ? O / L : 0.f);
       if (fused && tid == 0) {
         // every other block of this head has already read the old values (it took its ticket
@@ -332,6 +390,10 @@ __global__ void __launch_bounds__(kDecodeThreads) moa_decode_kernel(const Decode
     }
     __syncthreads();  // shared buffers are reused by the next head of this chunk
   }
+
+  // Barrier across the GPUs, inside the launch (out of line: it runs once per block at most and must not cost
+  // the streaming loop registers).
+  if (p.bar_world > 0 && rows_written > 0) decode_peer_barrier(&p, rows_written);   // uniform over the block
 }
 
 // Resident-block slots of the current device for this kernel (kept per device ordinal: one process may
@@ -375,7 +437,7 @@ struct WsLayout {
 };
 inline WsLayout ws_layout(int B, int H, int D, int64_t S, int chunk) {
   WsLayout w;
-  w.ticket_bytes = round_up((int64_t)B * H * 4, 256);
+  w.ticket_bytes = round_up((int64_t)B * H * 4 + 4, 256);   // tickets + the rows-written counter of the barrier
   w.nchunks = (S + chunk - 1) / chunk;
   w.slots_per_batch = w.nchunks + H;
   w.total = w.ticket_bytes + (int64_t)B * w.slots_per_batch * (D + 4) * 4;
@@ -396,6 +458,7 @@ struct DecodeCall {
   void* workspace; int64_t workspace_bytes; int chunk; cudaStream_t stream;
   const void* rope_cos; const void* rope_sin;
   void* const* out_peers; int n_out_peers;
+  void* const* bar_flags; int bar_rank, bar_world; uint32_t* bar_epoch; int64_t bar_limit; int32_t* bar_status;
 };
 
 // Validates the arguments, lays out the workspace and launches the kernel.
@@ -432,6 +495,20 @@ int decode_launch_with_scratch(const DecodeCall& a) {
   p.head_start = a.head_start; p.valid_len = a.valid_len;
   p.update_index = a.update_index; p.mask_cache = a.mask_cache; p.static_size = a.static_size; p.kv_len = a.kv_len;
   p.rope_cos = a.rope_cos; p.rope_sin = a.rope_sin;
+  p.bar_world = 0; p.bar_rank = 0; p.bar_epoch = nullptr; p.bar_limit = 0; p.bar_status = nullptr;
+  for (int g = 0; g < kMaxOutPeers; ++g) p.bar_flags[g] = nullptr;
+  if (a.bar_flags != nullptr) {
+    MOA_REQUIRE(a.bar_world >= 1 && a.bar_world <= kMaxOutPeers && a.bar_rank >= 0 && a.bar_rank < a.bar_world,
+                "decode_gather: the barrier serves 1..8 ranks");
+    MOA_REQUIRE(a.bar_epoch != nullptr && a.bar_status != nullptr, "decode_gather: the barrier needs its call counter and status words");
+    MOA_REQUIRE(a.bar_limit > 0 && a.bar_limit <= 20000000000ll, "decode_gather: barrier limit must be within (0, 2e10] cycles");
+    for (int g = 0; g < a.bar_world; ++g) {
+      MOA_REQUIRE(a.bar_flags[g] != nullptr, "decode_gather: null flag pointer");
+      p.bar_flags[g] = reinterpret_cast<uint32_t*>(a.bar_flags[g]);
+    }
+    p.bar_world = a.bar_world; p.bar_rank = a.bar_rank; p.bar_epoch = a.bar_epoch; p.bar_limit = (long long)a.bar_limit;
+    p.bar_status = a.bar_status;
+  }
   p.B = a.B; p.H = a.H; p.S = a.S; p.scale_log2 = a.sm_scale * 1.4426950408889634f;
   p.tickets = reinterpret_cast<int*>(a.workspace);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a.workspace) + w.ticket_bytes);
@@ -463,6 +540,7 @@ static moa::DecodeCall make_call(MOA_DECODE_ARGS_DECL, void* workspace, int64_t 
   a.static_size = static_size; a.kv_len = kv_len; a.B = B; a.H = H; a.D = D; a.S = S; a.sm_scale = sm_scale;
   a.dtype = dtype; a.out_f32 = out_f32; a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.chunk = chunk;
   a.stream = (cudaStream_t)stream; a.rope_cos = nullptr; a.rope_sin = nullptr; a.out_peers = nullptr; a.n_out_peers = 0;
+  a.bar_flags = nullptr; a.bar_rank = 0; a.bar_world = 0; a.bar_epoch = nullptr; a.bar_limit = 0; a.bar_status = nullptr;
   return a;
 }
 #define MOA_DECODE_ARGS_PASS                                                                                     \
@@ -498,13 +576,18 @@ int moa_decode_rope_fwd(MOA_DECODE_ARGS_DECL, const void* rope_cos, const void* 
 }
 
 int moa_decode_gather_fwd(MOA_DECODE_ARGS_DECL, const void* rope_cos, const void* rope_sin, void* const* out_peers,
-                          int n_out_peers, void* workspace, int64_t workspace_bytes, int chunk, moa_stream_t stream) {
+                          int n_out_peers, void* const* barrier_flags, int rank, int world, uint32_t* epoch_counter,
+                          int64_t limit_cycles, int32_t* barrier_status, void* workspace, int64_t workspace_bytes,
+                          int chunk, moa_stream_t stream) {
   MOA_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "decode_gather: rope_cos and rope_sin go together");
   moa::DecodeCall a = make_call(MOA_DECODE_ARGS_PASS, workspace, workspace_bytes, chunk, stream);
   a.rope_cos = rope_cos;
   a.rope_sin = rope_sin;
   a.out_peers = out_peers;
   a.n_out_peers = n_out_peers;
+  a.bar_flags = barrier_flags;
+  a.bar_rank = rank; a.bar_world = world; a.bar_epoch = epoch_counter; a.bar_limit = limit_cycles;
+  a.bar_status = barrier_status;
   return moa::decode_launch_with_scratch(a);
 }
 

@@ -145,8 +145,10 @@ class PeerGather:
     device memory that the other ranks of the node map into their address space (CUDA IPC).
     ``decode_and_gather`` runs the fused decode step with ``out`` = this rank's head slice of its own buffer
     and ``out_peers`` = the same slice of every other rank's buffer (``moa_decode_gather_fwd``: plain stores over
-    NVLink, nothing is loaded from a peer), then a barrier kernel (``moa_peer_barrier``) after which the buffer
-    holds all heads in shard order on every rank.  Two buffers are enough: a rank that is writing buffer
+    NVLink, nothing is loaded from a peer); the block that writes the launch's last row then publishes the call
+    number to every rank and waits for theirs, so that when the kernel has finished the buffer holds all heads in
+    shard order on every rank.  (``targets()`` + ``barrier()`` are the same thing as two launches, for callers
+    that bring their own kernel.)  Two buffers are enough: a rank that is writing buffer
     ``k`` of call ``c + 2`` has passed the barrier of call ``c + 1``, which every other rank enters only after
     its ``o_proj`` of call ``c`` has read buffer ``k``.  Calls must be made by all ranks in the same order.
 
@@ -250,13 +252,17 @@ class PeerGather:
 
     def decode_and_gather(self, cache, query_states: Tensor, key_states: Tensor, value_states: Tensor,
                           layer_idx: int, sm_scale: float, rope=None) -> Tensor:
-        """``StaticCircularCache.decode_attention`` on this rank's heads with the gather folded in: returns
-        ``(B, 1, H, D)`` with all ranks' heads in shard order."""
+        """``StaticCircularCache.decode_attention`` on this rank's heads with the gather folded in — one launch:
+        the kernel stores its rows into every rank's buffer and its last block runs the cross-rank barrier.
+        Returns ``(B, 1, H, D)`` with all ranks' heads in shard order."""
         out, peers = self.targets()
-        with _lib.nvtx_range("moa_b200.decode_and_gather"):
-            cache.decode_attention(query_states, key_states, value_states, layer_idx, sm_scale, out=out, rope=rope,
-                                   out_peers=peers)
-            return self.barrier()
+        full = self.buffers[self.epoch & 1]
+        self.epoch += 1
+        cache.decode_attention(query_states, key_states, value_states, layer_idx, sm_scale, out=out, rope=rope,
+                               out_peers=peers,
+                               barrier=(self._flag_ptrs, self.sh.rank, self.sh.world_size, self._calls.data_ptr(),
+                                        self.limit_cycles, self.status.data_ptr()))
+        return full
 
     def check(self) -> None:
         """Synchronises and raises if a barrier gave up waiting for a rank."""

@@ -348,3 +348,48 @@ def test_heads_without_rows_get_zero_output():
     moa_b200.sparse_decode(q.cuda(), k.cuda(), v.cuda(), hs.cuda(), valid.cuda(), 0.1, out=out)
     assert torch.isfinite(out).all() and out[:, :, 1].abs().sum() == 0
     _close(out, orc.decode_attention_fp32(q, k, v, hs, valid, 0.1), torch.float16, "zero-capacity head")
+
+
+def test_gather_launch_with_its_barrier_on_one_gpu():
+    """The decode launch that also delivers its rows and ends with the cross-rank barrier, on one GPU:
+    (1) a one-rank group: same result as the plain fused step, call after call, the device-side call counter
+    advances; (2) a pretended two-rank group whose other rank never arrives: the bounded wait inside the kernel
+    runs out, the status words say who was missing, the output is still right and the next launch works."""
+    import ctypes
+    gen = torch.Generator().manual_seed(41)
+    B, Dh = 3, 128
+    caps = [320, 576, 128, 1088]
+    H = len(caps)
+    kp = torch.randn(B, H, 700, Dh, generator=gen).half().cuda()
+    vp = torch.randn(B, H, 700, Dh, generator=gen).half().cuda()
+    c_ref = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", torch.float16)
+    c_one = moa_b200.StaticCircularCache([caps], B, Dh, [[64] * H], "cuda", torch.float16)
+    c_ref.update(kp, vp, 0)
+    c_one.update(kp, vp, 0)
+    sh = moa_b200.HeadSharding(caps, 1, 0)
+    pg = moa_b200.PeerGather(sh, B, Dh, torch.float16, "cuda")
+    for step in range(3):
+        q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen).half().cuda() for _ in range(3))
+        want = c_ref.decode_attention(q, k1, v1, 0, 0.09)
+        got = pg.decode_and_gather(c_one, q, k1, v1, 0, 0.09)
+        assert torch.equal(got, want)
+    pg.check()
+    assert pg._calls.item() == 3
+    pg.close()
+
+    flags0 = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags1 = torch.zeros(8, dtype=torch.int32, device="cuda")       # the absent rank's (nobody reads them)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    calls = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(flags0.data_ptr(), flags1.data_ptr())
+    q, k1, v1 = (torch.randn(B, H, 1, Dh, generator=gen).half().cuda() for _ in range(3))
+    want = c_ref.decode_attention(q, k1, v1, 0, 0.09)
+    got = c_one.decode_attention(q, k1, v1, 0, 0.09,
+                                 barrier=(ptrs, 0, 2, calls.data_ptr(), 20_000_000, status.data_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert status.tolist() == [21, 1, 1, 0] and calls.item() == 1
+    assert flags0.tolist()[:2] == [1, 0] and flags1.tolist()[0] == 1
+    want = c_ref.decode_attention(q, k1, v1, 0, 0.09)                # the rows-written counter was put back to zero
+    got = c_one.decode_attention(q, k1, v1, 0, 0.09)
+    assert torch.equal(got, want)
