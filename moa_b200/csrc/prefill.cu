@@ -370,13 +370,7 @@ struct TileWork {
   bool active1;       // the second 128-row tile exists
   TileBlocks tb;
 };
-// WARP: called by a whole converged warp.  The unit and the two values loaded from the plan are then passed
-// through a lane-0 broadcast, which lets the compiler see that everything derived from them is the same in
-// all lanes and keep it in uniform registers — what the MMA issuers' descriptors and addresses need (values
-// read from shared or global memory are not known to be uniform otherwise, and the issue path gets slower).
-template <bool WARP>
 __device__ __forceinline__ TileWork tile_work(int unit, const PrefillParams& p) {
-  if (WARP) unit = __shfl_sync(0xffffffffu, unit, 0);
   const TileCoord c = tile_coord(unit, p);
   TileWork w;
   w.b = c.b;
@@ -385,10 +379,6 @@ __device__ __forceinline__ TileWork tile_work(int unit, const PrefillParams& p) 
   w.nb = (int)((p.N + kBN - 1) / kBN);
   w.sink_b = p.sink_blocks[c.h];
   w.local_b = p.local_blocks[c.h];
-  if (WARP) {
-    w.sink_b = __shfl_sync(0xffffffffu, w.sink_b, 0);
-    w.local_b = __shfl_sync(0xffffffffu, w.local_b, 0);
-  }
   w.active1 = (int64_t)(w.t0 + 1) * kBM < p.N;
   w.tb = tile_blocks(w.t0, w.active1 ? w.t0 + 1 : w.t0, w.nb, w.sink_b, w.local_b);
   w.nkv = w.tb.count();
@@ -418,7 +408,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   static_assert(DH == 64 || DH == 128, "head_dim");
 
   // the block's first unit is its own index: fetch its head's plan while the barriers and TMEM are set up
-  const TileWork w_first = tile_work<true>((int)blockIdx.x, p);
+  const TileWork w_first = tile_work((int)blockIdx.x, p);
   if (warp == 8 && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -489,7 +479,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         } else if (n > 0) {
           break;
         }
-        const TileWork w = (n == 0) ? w_first : tile_work<false>(unit, p);
+        const TileWork w = (n == 0) ? w_first : tile_work(unit, p);
         mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
 #pragma unroll
         for (int hf = 0; hf < NH; ++hf) {
@@ -599,7 +589,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       } else if (n > 0) {
         break;
       }
-      const TileWork w = (n == 0) ? w_first : tile_work<true>(unit, p);
+      const TileWork w = (n == 0) ? w_first : tile_work(unit, p);
       const int nkv = w.nkv;
       const TileSeen seen = tile_seen(x == 0 || w.active1, w.t0 + x, w.tb, w.nb, w.local_b);
 
@@ -760,7 +750,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       } else if (n > 0) {
         break;
       }
-      const TileWork w = (n == 0) ? w_first : tile_work<true>(unit, p);
+      const TileWork w = (n == 0) ? w_first : tile_work(unit, p);
       const int tq = w.t0 + x;
       const TileSeen seen = tile_seen(x == 0 || w.active1, tq, w.tb, w.nb, w.local_b);
       const int64_t i_tok = (int64_t)tq * kBM + row;        // query position
