@@ -66,7 +66,10 @@ constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + 2 * kQBytes;
 constexpr int kSmemV = kSmemK + kStages * kKBytes;
 constexpr int kSmemCtl = kSmemV + kStages * kKBytes;
-constexpr int kSmemBytes = kSmemCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
+constexpr int kSmemStage = kSmemCtl + 512;  // epilogue staging: 32 rows of 128 B for each of the 8 softmax warps
+constexpr int kStageBytes = 32 * 128;
+constexpr int kSmemBytes = kSmemStage + 8 * kStageBytes + 1024;  // + slack for 1024-byte alignment
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of one block");
 
 // the running max is only moved when a block exceeds it by more than this (log2 units)
 constexpr float kLazyMaxSlack = 8.f;
@@ -863,21 +866,35 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (!ok) break;
         tc_fence_after();
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-        const bool store = i_tok < p.N;
-        uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                        ((int64_t)w.b * p.o_sb + i_tok * p.o_sn + (int64_t)w.h * p.o_sh) * (OUT_F32 ? 4 : 2);
+        // Thread r holds row r, and rows lie a whole token apart in the output: stored from here, every store
+        // instruction would touch 32 lines.  Instead each warp turns its 32 rows x 128 bytes around in shared
+        // memory (16-byte pieces, XOR-swizzled by the row so that neither side has bank conflicts) and stores
+        // whole 128-byte lines, four rows per instruction.
+        constexpr int kEs = OUT_F32 ? 4 : 2;
+        constexpr int kFlushCols = 128 / kEs;               // output columns in 128 bytes
+        // (the addresses are derived here, behind an opaque copy of the thread's indices, so that the compiler does
+        // not keep them in registers across the step loop of the persistent form)
+        int ln = lane, wp = warp;
+        asm volatile("" : "+r"(ln), "+r"(wp));
+        uint8_t* const stage = smem + kSmemStage + wp * kStageBytes;
+        uint8_t* const mine = stage + ln * 128;
+        const int sw = ln & 7, piece = ln & 7, sub = ln >> 3;
+        const int64_t tok0 = (int64_t)tq * kBM + (wp & 3) * 32 + sub;   // row of this lane's first store
+        uint8_t* const obase = reinterpret_cast<uint8_t*>(p.out) +
+                               ((int64_t)w.b * p.o_sb + tok0 * p.o_sn + (int64_t)w.h * p.o_sh) * kEs + piece * 16;
 #pragma unroll 1
-        for (int c0 = 0; c0 < DH; c0 += 32) {
-          uint32_t ov[32];
-          tmem_ld32(lane_base + col_o(x) + c0, ov);
-          tmem_wait_ld();
-          if (store) {
+        for (int c0 = 0; c0 < DH; c0 += kFlushCols) {
+#pragma unroll
+          for (int cc = 0; cc < kFlushCols; cc += 32) {
+            uint32_t ov[32];
+            tmem_ld32(lane_base + col_o(x) + c0 + cc, ov);
+            tmem_wait_ld();
             if (OUT_F32) {
 #pragma unroll
               for (int c = 0; c < 32; c += 4) {
                 float4 f = make_float4(__uint_as_float(ov[c]) * inv_l, __uint_as_float(ov[c + 1]) * inv_l,
                                        __uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
-                *reinterpret_cast<float4*>(orow + (c0 + c) * 4) = f;
+                *reinterpret_cast<float4*>(mine + (((c >> 2) ^ sw) << 4)) = f;
               }
             } else {
 #pragma unroll
@@ -887,10 +904,18 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 uo.y = Cvt<T>::pack(__uint_as_float(ov[c + 2]) * inv_l, __uint_as_float(ov[c + 3]) * inv_l);
                 uo.z = Cvt<T>::pack(__uint_as_float(ov[c + 4]) * inv_l, __uint_as_float(ov[c + 5]) * inv_l);
                 uo.w = Cvt<T>::pack(__uint_as_float(ov[c + 6]) * inv_l, __uint_as_float(ov[c + 7]) * inv_l);
-                *reinterpret_cast<uint4*>(orow + (c0 + c) * 2) = uo;
+                *reinterpret_cast<uint4*>(mine + ((((cc + c) >> 3) ^ sw) << 4)) = uo;
               }
             }
           }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + sub;                      // row of the warp's 32
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
+            if (tok0 + it * 4 < p.N) *reinterpret_cast<uint4*>(obase + (int64_t)(it * 4) * p.o_sn * kEs + c0 * kEs) = val;
+          }
+          __syncwarp();
         }
         // the next super-tile's first O += P V overwrites O; it is issued only after every thread of this
         // tile has arrived with its first P, i.e. after these loads
