@@ -63,7 +63,7 @@ MIN_REGION_S = 0.25        # GPU time the repeated blocks should add up to
 # algorithmic bytes; traffic grows in proportion to the rows streamed (decode) and to the tensor sizes
 # (prefill: Q, K, V read once, O written once).
 DECODE_DRAM_TRAFFIC_RATIO = 1.027
-PREFILL_DRAM_TRAFFIC_RATIO = 0.986
+PREFILL_DRAM_TRAFFIC_RATIO = 0.985
 
 
 def config1_caps(seed: int):
