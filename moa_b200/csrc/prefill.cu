@@ -483,13 +483,18 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           break;
         }
         const TileWork w = (n == 0) ? w_first : tile_work(unit, p);
-        mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
+        // A super-tile that visits no KV block at all (a head without sink and window at the ragged end of the
+        // sequence) loads nothing: nobody would wait for its Q, and a copy must never be in flight when the block
+        // ends, nor may q_full be armed again before its previous phase has completed.
+        if (w.nkv > 0) {
+          mbar_expect_tx(&ctl->q_full, 2 * NH * kQPanel);
 #pragma unroll
-        for (int hf = 0; hf < NH; ++hf) {
-          tma_load_4d(smem + kSmemQ + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, w.t0 * kBM, w.h, w.b);
-          tma_load_4d(smem + kSmemQ + kQBytes + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, (w.t0 + 1) * kBM, w.h, w.b);
+          for (int hf = 0; hf < NH; ++hf) {
+            tma_load_4d(smem + kSmemQ + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, w.t0 * kBM, w.h, w.b);
+            tma_load_4d(smem + kSmemQ + kQBytes + hf * kQPanel, &map_q, &ctl->q_full, 64 * hf, (w.t0 + 1) * kBM, w.h, w.b);
+          }
+          ++q_issued;
         }
-        q_issued = n + 1;
         // V lags K by one tile: it is needed one MMA step later.  A stage is reused once both
         // tiles' issuers have handed it back.
         for (int u = 0; ok && u <= w.nkv; ++u) {
@@ -573,6 +578,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* const v_empty = ctl->v_empty[x];
     uint32_t ring = 0;   // K/V ring entries of the super-tiles before this one
     uint32_t sbase = 0;  // S/P buffers this tile has used before this super-tile
+    uint32_t q_loads = 0;  // super-tiles before this one whose Q was loaded (those that visit any KV block)
     bool ok = true;
     auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
       const bool mine = mbar_wait(bar, parity, ctl, p.status, code);
@@ -650,7 +656,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
       if (seen.total > 0) {
         skip_both(0, seen.entry(0));
-        if (ok) wait(&ctl->q_full, n & 1, kWaitQ);
+        if (ok) wait(&ctl->q_full, q_loads & 1, kWaitQ);
         if (ok) issue_qk(0);
         if (ok && seen.total > 1) {
           skip_k(seen.entry(0) + 1, seen.entry(1));
@@ -728,6 +734,7 @@ moa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       ring += (uint32_t)nkv;
       sbase += (uint32_t)seen.total;
+      q_loads += nkv > 0 ? 1u : 0u;
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue

@@ -254,6 +254,27 @@ def test_heads_that_see_nothing_give_zero_rows():
     _close(out, orc.prefill_attention_fp32(q, k, v, 0.1, [0, 1], [0, 2]), "head 0 sees nothing")
 
 
+@pytest.mark.parametrize("B,H,N", [(2, 3, 513), (1, 3, 17), (1, 41, 2061)])
+def test_super_tiles_that_visit_no_block_load_nothing(B, H, N):
+    """At most 64 rows in the last super-tile, under a head without sink and window: that super-tile visits no KV
+    block at all, so nobody waits for its Q.  The kernel must not load it (a copy in flight when the block ends,
+    or, in the persistent form, the Q barrier armed twice in one phase).  2061 tokens of 41 heads are 369 units:
+    the persistent form.  Launched repeatedly; rows of the blind heads are zero, the rest matches the oracle."""
+    gen = torch.Generator().manual_seed(N)
+    q, k, v = (torch.randn(B, H, N, 128, generator=gen).half() for _ in range(3))
+    sink_b = [(0, 1, 0)[h % 3] for h in range(H)]
+    local_b = [(0, 3, 0)[h % 3] if h % 6 else 7 for h in range(H)]
+    sm = 128 ** -0.5
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    sb, lb = (torch.tensor(x, dtype=torch.int32).cuda() for x in (sink_b, local_b))
+    outs = [moa_b200.sparse_prefill(qd, kd, vd, sm, sb, lb) for _ in range(25)]
+    moa_b200.check_device_status()
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    blind = [h for h in range(H) if sink_b[h] == 0 and local_b[h] == 0]
+    assert blind and outs[0][:, :, blind].abs().sum() == 0
+    _close(outs[0], orc.prefill_attention_fp32(q, k, v, sm, sink_b, local_b), f"blind heads at a ragged end, N={N}")
+
+
 def test_short_prompt_without_sizes_is_dense_causal():
     gen = torch.Generator().manual_seed(4)
     q, k, v = (torch.randn(1, 2, 40, 128, generator=gen).half() for _ in range(3))

@@ -322,8 +322,12 @@ class CountBarrier(Barrier):
             self.pending, self.done = 0, self.done + 1
 
 
-def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
-    """units: [(n, sink_b, local_b, st), ...] in the order one block receives them."""
+def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True, q_load_every_unit=False):
+    """units: [(n, sink_b, local_b, st), ...] in the order one block receives them.
+
+    The producer's bulk copies are modelled as what they are: the producer *arms* a "full" barrier (expect-tx)
+    and the copy lands at some later, random time.  A barrier may only be armed when its previous phase has
+    completed, and no copy may be in flight when the block's roles have all finished."""
 
     def hand_back(bar):
         if isinstance(bar, CountBarrier):
@@ -347,6 +351,20 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
     slot_value = [None, None]
     finished = {"o_read": [0, 0], "o_written_first": [0, 0]}
 
+    in_flight = []
+    armed = {}
+
+    def arm(bar):
+        assert armed.get(bar.name, 0) == bar.done, f"{bar.name} armed again before its previous phase completed"
+        armed[bar.name] = bar.done + 1
+        in_flight.append(bar)
+
+    def copies():
+        while True:
+            if in_flight and rng.randint(3) == 0:
+                in_flight.pop(rng.randint(len(in_flight))).done += 1
+            yield
+
     def wait(bar, need):
         while not bar.look(need):
             yield
@@ -368,18 +386,19 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
             if n > 0 and not q_wait_first:
                 while not (qempty[0].look(n) and qempty[1].look(n)):
                     yield
-            qfull.done += 1
+            if nkv > 0 or q_load_every_unit:
+                arm(qfull)
             for u in range(nkv + 1):
                 if u < nkv:
                     g = ring + u
                     while not (kempty[0][g % STAGES].look(g // STAGES) and kempty[1][g % STAGES].look(g // STAGES)):
                         yield
-                    kfull[g % STAGES].done += 1
+                    arm(kfull[g % STAGES])
                 if u >= 1:
                     g = ring + u - 1
                     while not (vempty[0][g % STAGES].look(g // STAGES) and vempty[1][g % STAGES].look(g // STAGES)):
                         yield
-                    vfull[g % STAGES].done += 1
+                    arm(vfull[g % STAGES])
             ring += nkv
 
     def take_unit(n):
@@ -390,7 +409,7 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
         return unit
 
     def issuer(x):
-        ring = sbase = 0
+        ring = sbase = q_loads = 0
         n = 0
         while True:
             unit = yield from take_unit(n)
@@ -425,7 +444,7 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
 
             if total > 0:
                 yield from skip_both(0, sn[0])
-                yield from wait(qfull, n + 1)
+                yield from wait(qfull, (n if q_load_every_unit else q_loads) + 1)
                 yield from issue_qk(0)
                 if total > 1:
                     yield from skip("k", sn[0] + 1, sn[1])
@@ -463,6 +482,7 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
                 yield from skip_both(sn[-1] + 1, nkv)
             ring += nkv
             sbase += total
+            q_loads += 1 if nkv > 0 else 0
             n += 1
 
     def softmax(x):
@@ -490,11 +510,11 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
             n_o += 1 if total > 0 else 0
             n += 1
 
-    agents = [producer(), issuer(0), issuer(1), softmax(0), softmax(1)]
+    agents = [producer(), issuer(0), issuer(1), softmax(0), softmax(1), copies()]
     alive = list(range(len(agents)))
     everything = (kfull, vfull, kempty, vempty, sfull, pfull, [pvdone], [ofull], [[qfull] + qempty], [tfull], [tempty])
     idle_rounds = 0
-    while alive:
+    while alive != [5]:                       # until every role of the block has finished
         k = alive[rng.randint(len(alive))]
         before = _snapshot(*everything)
         try:
@@ -502,7 +522,8 @@ def simulate_persistent(units, rng, q_empty_per_issuer=True, q_wait_first=True):
         except StopIteration:
             alive.remove(k)
         idle_rounds = idle_rounds + 1 if _snapshot(*everything) == before else 0
-        assert idle_rounds < 6000, "nobody makes progress"
+        assert idle_rounds < 20000, "nobody makes progress"
+    assert not in_flight, f"{in_flight[0].name}: a copy is still in flight when the block ends"
     assert finished["o_read"] == finished["o_written_first"]
 
 
@@ -512,7 +533,7 @@ def test_persistent_sequence_of_super_tiles_keeps_every_barrier_unambiguous():
     overwritten before the previous epilogue has read it.  Includes super-tiles in which one tile or both see
     nothing, single-entry tiles, and ragged last super-tiles."""
     shapes = [(4096, 1, 100), (4096, 1, 7), (2048, 2, 3), (1000, 0, 2), (5000, 3, 16), (200, 1, 1), (64, 0, 0),
-              (700, 0, 0), (300, 1, 0), (129, 1, 1), (256, 1, 40)]
+              (700, 0, 0), (300, 1, 0), (129, 1, 1), (256, 1, 40), (513, 0, 0), (17, 0, 0)]
     for seed in range(12):
         rng = np.random.RandomState(100 + seed)
         units = []
@@ -525,16 +546,34 @@ def test_persistent_sequence_of_super_tiles_keeps_every_barrier_unambiguous():
 def test_the_persistent_model_catches_a_shared_q_hand_back_barrier():
     """With one "Q is free" barrier of count 2 shared by the two issuers, an issuer that has nothing to do in the
     next super-tile arrives twice in a row and completes the phase on its own; the producer then overwrites Q
-    (and completes a second phase of q_full) while the other issuer still waits for the first (when, in addition,
-    the next super-tile is published before the hand-back has been seen).  The model must notice."""
+    (and completes a second phase of q_full, or sees q_empty two phases on) while the other issuer still waits for
+    the first (when, in addition, the next super-tile is published before the hand-back has been seen).  The model
+    must notice."""
     units = [(700, 0, 0, 1), (64, 0, 0, 0), (2048, 2, 3, 4), (2048, 2, 3, 1)]
     caught = 0
     for seed in range(40):
         try:
             simulate_persistent(units, np.random.RandomState(seed), q_empty_per_issuer=False, q_wait_first=False)
         except AssertionError as exc:
-            caught += "q_full" in str(exc)
+            caught += "q_full" in str(exc) or "q_empty" in str(exc)
     assert caught > 0
+
+
+def test_the_persistent_model_catches_a_q_load_nobody_waits_for():
+    """A super-tile that visits no KV block (no sink, no window, at most 64 rows at the ragged end) has no reader of
+    Q.  Loading its Q all the same leaves a copy in flight when the block ends, or has q_full armed a second time
+    inside one phase when another super-tile follows at once.  The model must notice both; the kernel therefore
+    loads Q only for super-tiles that visit something and counts q_full's phases by those."""
+    in_flight = armed_twice = 0
+    for seed in range(40):
+        for units in ([(2048, 2, 3, 4), (64, 0, 0, 0)], [(64, 0, 0, 0), (513, 0, 0, 2), (2048, 2, 3, 1)]):
+            try:
+                simulate_persistent(units, np.random.RandomState(seed), q_load_every_unit=True)
+            except AssertionError as exc:
+                in_flight += "in flight" in str(exc)
+                armed_twice += "armed again" in str(exc)
+            simulate_persistent(units, np.random.RandomState(seed))          # the kernel's rule passes
+    assert in_flight > 0 and armed_twice > 0
 
 
 def test_the_persistent_model_catches_publishing_before_q_is_handed_back():
