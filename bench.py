@@ -548,10 +548,15 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
         except Exception as exc:
             peer_error = f"{type(exc).__name__}: {exc}"[:300]
     if pg is not None:
-        fill_rings_directly(cache, 0, device, mine_ids, 131072, 4000)
-        fused = pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
-        pg.check()
-        fused_equal = bool(torch.equal(fused, gathered))
+        try:        # a barrier that gave up on any rank sends every rank down the NCCL path together
+            fill_rings_directly(cache, 0, device, mine_ids, 131072, 4000)
+            fused = pg.decode_and_gather(cache, trio[0], trio[1], trio[2], 0, sm)
+            pg.check(collective=True)
+            fused_equal = bool(torch.equal(fused, gathered))
+        except moa_b200.MoaError as exc:
+            peer_error = f"{type(exc).__name__}: {exc}"[:300]
+            pg.close()
+            pg = None
     probe = None
     if rank == 0:
         worst = 0.0
@@ -615,7 +620,7 @@ def layer_leg(device, dist, world: int, rank: int, steps: int = 64, warmup: int 
         ms, _ = time_blocks(fn, steps, device, dist, min_blocks=5, min_region_s=0.1)
         proj[name + "_us"] = statistics.median(ms) / steps * 1e3
     if pg is not None:
-        pg.check()
+        pg.check(collective=True)
         pg.close()
 
     kv_bytes_all = moa_b200.decode_bytes(Bl, caps, Dl, 2)
@@ -703,16 +708,24 @@ def model_leg(device, dist, world: int, rank: int, steps: int = 8, warmup: int =
     ms, _ = time_blocks(step_graph, steps, device, dist, min_blocks=3, min_region_s=0.2)
     per_step = statistics.median(ms) / steps
     del graph
+    peer_error = None
     if pg is not None:
-        pg.check()
+        try:        # a barrier that gave up on any rank: every rank reports the NCCL figure instead
+            pg.check(collective=True)
+        except moa_b200.MoaError as exc:
+            peer_error = f"{type(exc).__name__}: {exc}"[:300]
+            per_step = per_step_eager = per_step_nccl
         pg.close()
+        if peer_error is not None:
+            pg = None
     weights = sum(prm.numel() for name, prm in model.named_parameters()
                   if prm.dim() > 1 and "embed_tokens" not in name) * 2
     return {"workload": f"config2: Vicuna-7B-16k architecture, random weights, decode B{batch} at {context} context, "
                         f"{layers} layers, heads sharded over {world} GPU(s)",
             "tokens_per_s": batch / (per_step * 1e-3), "ms_per_step": per_step,
             "how": "one CUDA graph per decode step (all layers)" + (", gather and barrier inside the decode launch"
-                   if pg is not None else (", NCCL all-gather" if world > 1 else "")),
+                   if pg is not None else (", NCCL all-gather" if world > 1 else "")) +
+                   (f" (eager launches; the peer gather was abandoned: {peer_error})" if peer_error else ""),
             "ms_per_step_eager_launches": per_step_eager,
             "ms_per_step_eager_nccl_allgather": per_step_nccl if world > 1 else None,
             "kv_bytes_per_step_per_gpu": kv_bytes, "weight_bytes_per_step_per_gpu": weights,

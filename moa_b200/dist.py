@@ -5,8 +5,8 @@ exchange inside attention.  Where a whole layer runs, the per-rank outputs ``(B,
 all-gathered into ``(B, q, H, D)`` before ``o_proj`` (NCCL over NVLink; ``gloo`` on CPU in the tests).
 One process per GPU (``torchrun``).  ``HeadSharding.all_gather`` is the plain collective; ``PeerGather`` is
 the decode path's fused form: the decode kernel stores its output rows straight into every rank's
-``(B, 1, H, D)`` buffer over NVLink and a barrier kernel orders the stores before the reads, so the step has
-no collective launch and no copy after it.
+``(B, 1, H, D)`` buffer over NVLink and ends with a cross-rank barrier that orders the stores before the reads,
+so the step has no collective launch and no copy after it.
 
 The step after attention, ``o_proj`` (``MoA/models/llama/modeling_llama.py:329-330`` in the reference),
 comes in two forms here: the gathered one (all-gather the head shards, then the full projection on every
@@ -264,14 +264,25 @@ class PeerGather:
                                         self.limit_cycles, self.status.data_ptr()))
         return full
 
-    def check(self) -> None:
-        """Synchronises and raises if a barrier gave up waiting for a rank."""
+    def check(self, collective: bool = False) -> None:
+        """Synchronises and raises if a barrier gave up waiting for a rank.  ``collective=True`` (every rank of the
+        group calls it): all ranks raise when any rank's barrier gave up, so that the ranks of a job take the same
+        path afterwards."""
         torch.cuda.synchronize(self.device)
         words = self.status.tolist()
-        if words[0] != 0:
+        failed = words[0] != 0
+        elsewhere = False
+        if collective and self.sh.world_size > 1:
+            flag = torch.tensor([int(failed)], dtype=torch.int32, device=self.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.sh.group)
+            elsewhere = bool(flag.item()) and not failed
+        if failed:
             self.status.zero_()
             raise _lib.MoaError("moa_peer_barrier", 5, _lib.lib.moa_strerror(5).decode(),
                                 f"rank {words[3]} gave up waiting for rank {words[1]} at call {words[2]}")
+        if elsewhere:
+            raise _lib.MoaError("moa_peer_barrier", 5, _lib.lib.moa_strerror(5).decode(),
+                                "the barrier gave up on another rank of the group")
 
     def close(self) -> None:
         if self._own is None:

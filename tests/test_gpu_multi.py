@@ -70,6 +70,19 @@ def _worker(rank, world, port, ret):
             got = pg.decode_and_gather(local3, *args)
             assert torch.equal(got, want)
         pg.check()
+        pg.check(collective=True)
+        # A failure reported on one rank only (set by the host here, no kernel involved): the collective form of
+        # the check raises on every rank, so that the ranks of a job abandon the fused gather together.
+        if rank == 0:
+            pg.status[0] = 21
+        try:
+            pg.check(collective=True)
+            raised = False
+        except moa_b200.MoaError as exc:
+            raised = True
+            assert ("gave up waiting" in str(exc)) == (rank == 0)
+        assert raised
+        pg.check(collective=True)         # the words were cleared: the next check passes on every rank
         pg.close()
 
         # model level: head-sharded model (collective gather, then the fused gather) against the unsharded model
