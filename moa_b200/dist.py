@@ -205,12 +205,12 @@ class PeerGather:
                 except Exception as exc:
                     failure = exc
             if G > 1:
-                verdict: List[Optional[bool]] = [None] * G
-                dist.all_gather_object(verdict, failure is None, group=sharding.group)
-                if failure is None and not all(verdict):
+                outcomes: List[Optional[bool]] = [None] * G
+                dist.all_gather_object(outcomes, failure is None, group=sharding.group)
+                if failure is None and not all(outcomes):
                     failure = RuntimeError("PeerGather: another rank could not map the buffers (CUDA IPC between "
                                            f"the ranks' GPUs is needed); ranks that failed: "
-                                           f"{[g for g, ok in enumerate(verdict) if not ok]}")
+                                           f"{[g for g, ok in enumerate(outcomes) if not ok]}")
             if failure is not None:
                 for g, b in enumerate(self.bases):
                     if g != sharding.rank:
